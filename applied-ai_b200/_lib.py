@@ -1,0 +1,99 @@
+"""ctypes binding of libb200moe.so.
+
+The library is the only compute path of this package: if it cannot be loaded the
+import of any operator fails with an error that says so.  There is no fallback to
+torch or to the CPU.
+"""
+import ctypes
+import os
+import threading
+
+from . import build as _build
+
+_c_int = ctypes.c_int
+_c_i64 = ctypes.c_int64
+_c_vp = ctypes.c_void_p
+_c_sz = ctypes.c_size_t
+
+ERROR_NAMES = {
+    -1: "bad argument",
+    -2: "misaligned pointer or K * element size not a multiple of 16 bytes",
+    -3: "more than 1024 groups",
+    -4: "cuTensorMapEncodeTiled not available from the driver",
+    -5: "the driver rejected a tensor map",
+    -6: "current device is not a compute-capability 10.x GPU",
+    -7: "workspace too small or size beyond the supported maximum",
+}
+STATUS_NAMES = {
+    1: "invalid group sizes / expert ids (negative entry, sum(m_sizes) > rows of x, or id outside [0, E))",
+    16: "device-side wait ran out (TMA producer)",
+    17: "device-side wait ran out (MMA issuer, operand stage)",
+    18: "device-side wait ran out (MMA issuer, accumulator)",
+    19: "device-side wait ran out (epilogue)",
+    32: "kernel image not built for sm_100a",
+}
+
+# name -> argtypes; every function returns int.  Must list every symbol that
+# include/b200moe.h declares (a CPU test checks this).
+SIGNATURES = {
+    "b200moe_version": [],
+    "b200moe_grouped_gemm_bf16": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_i64, _c_i64,
+                                  _c_int, _c_int, _c_vp, _c_vp],
+    "b200moe_grouped_gemm_fp8_rowwise": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
+                                         _c_i64, _c_i64, _c_int, _c_vp, _c_vp],
+    "b200moe_route_workspace_bytes": [_c_int, _c_int, ctypes.POINTER(_c_sz)],
+    "b200moe_route": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp],
+    "b200moe_gather_rows": [_c_vp, _c_vp, _c_int, _c_vp, _c_int, _c_i64, _c_int, _c_vp],
+    "b200moe_swiglu": [_c_vp, _c_vp, _c_i64, _c_int, _c_vp],
+    "b200moe_combine_topk": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "b200moe_quant_1x128": [_c_vp, _c_int, _c_vp, _c_vp, _c_i64, _c_int, _c_vp],
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+class B200MoeError(RuntimeError):
+    """A C entry point returned a non-zero code."""
+
+
+def lib_path():
+    return _build.LIB_PATH
+
+
+def load(build_if_missing=True):
+    """Load (building first if needed and allowed) and return the ctypes library."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = _build.LIB_PATH
+        if not os.path.exists(path):
+            if not build_if_missing:
+                raise ImportError(f"{path} is missing; run `python applied-ai_b200/build.py`")
+            _build.build_library()
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as exc:
+            raise ImportError(f"cannot load {path}: {exc}. This package has no fallback path.") from exc
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError here = stale library
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+        _lib = lib
+        return lib
+
+
+def check(rc, what):
+    """Raise for a non-zero return code of entry point `what`."""
+    if rc == 0:
+        return
+    if rc < 0:
+        msg = ERROR_NAMES.get(rc, "unknown error")
+        exc = ValueError if rc == -3 else B200MoeError
+        raise exc(f"{what}: {msg} (code {rc})")
+    raise B200MoeError(f"{what}: CUDA error {rc}")
+
+
+def describe_status(code):
+    return STATUS_NAMES.get(int(code), f"unknown status {int(code)}")

@@ -1,0 +1,62 @@
+// Types shared by the translation units of libb200moe.so (not part of the public ABI).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200moe {
+
+// Values a kernel may leave in the caller's status word (0 = nothing to report).
+enum : int32_t {
+    kStatusBadGroupSizes = 1,     // a negative group size, or the sizes add up to more rows than x has
+    kStatusTimeoutProducer = 16,  // TMA producer gave up waiting for a free stage
+    kStatusTimeoutMmaFull = 17,   // MMA issuer gave up waiting for a filled stage
+    kStatusTimeoutMmaAcc = 18,    // MMA issuer gave up waiting for a drained accumulator
+    kStatusTimeoutEpilogue = 19,  // epilogue gave up waiting for a finished accumulator
+    kStatusWrongArch = 32,        // kernel image was not built for sm_100a
+};
+
+// Negative return codes of the C entry points (positive values are cudaError_t).
+enum : int {
+    kErrBadArgument = -1,
+    kErrAlignment = -2,
+    kErrTooManyGroups = -3,
+    kErrNoDriverEntry = -4,
+    kErrTensorMap = -5,
+    kErrWrongDevice = -6,
+    kErrTooLarge = -7,
+};
+
+struct GGParams {
+    const int32_t* m_sizes;
+    void* y;
+    const float* x_scale;
+    const float* w_scale;
+    int32_t* status;
+    long long ldy;                 // elements between consecutive rows of y
+    long long y_col_group_stride;  // first column of group g's block is g * this (0: all groups share columns)
+    int M, N, K, G;
+    int n_out;    // output columns per group (N, or N/2 with SwiGLU)
+    int n_tiles;  // column tiles per group
+};
+
+struct GGLaunch {
+    const void* x;
+    const void* w;
+    const int32_t* m_sizes;
+    void* y;
+    const float* x_scale;
+    const float* w_scale;
+    int32_t* status;
+    long long ldy;
+    long long y_col_group_stride;
+    int M, N, K, G;
+    int elem_bytes;  // 2 bf16, 1 e4m3
+    int scale_mode;  // 0 none, 1 row-wise
+    int epilogue;    // 0 plain, 1 SwiGLU
+    int cta_group;   // 0 auto, 1 or 2
+    cudaStream_t stream;
+};
+
+int grouped_gemm_launch(const GGLaunch& a);
+
+}  // namespace b200moe

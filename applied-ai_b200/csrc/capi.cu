@@ -1,0 +1,121 @@
+// extern "C" entry points of libb200moe.so; declarations and contracts are in
+// include/b200moe.h.  Each one validates its arguments on the host, enqueues kernels
+// on the caller's stream and returns a code; none allocates, synchronises or throws.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200moe.h"
+#include "b200moe_internal.h"
+#include "moe_kernels.h"
+
+using namespace b200moe;
+
+static_assert(B200MOE_EBADARG == kErrBadArgument && B200MOE_EALIGN == kErrAlignment &&
+                  B200MOE_ETOOMANYGROUPS == kErrTooManyGroups && B200MOE_ENODRIVER == kErrNoDriverEntry &&
+                  B200MOE_ETENSORMAP == kErrTensorMap && B200MOE_EWRONGDEVICE == kErrWrongDevice &&
+                  B200MOE_ETOOLARGE == kErrTooLarge,
+              "public and internal error codes must agree");
+static_assert(B200MOE_SBADSIZES == kStatusBadGroupSizes && B200MOE_STIMEOUT_FIRST == kStatusTimeoutProducer &&
+                  B200MOE_STIMEOUT_LAST == kStatusTimeoutEpilogue && B200MOE_SWRONGARCH == kStatusWrongArch,
+              "public and internal status codes must agree");
+
+extern "C" {
+
+int b200moe_version(void) { return 1; }
+
+int b200moe_grouped_gemm_bf16(const void* x, const void* w, const int32_t* m_sizes, void* y, int M, int N, int K,
+                              int G, int64_t ldy, int64_t y_col_group_stride, int epilogue, int cta_group,
+                              int32_t* status, b200moe_stream_t stream) {
+    GGLaunch a{};
+    a.x = x;
+    a.w = w;
+    a.m_sizes = m_sizes;
+    a.y = y;
+    a.status = status;
+    a.ldy = ldy;
+    a.y_col_group_stride = y_col_group_stride;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.G = G;
+    a.elem_bytes = 2;
+    a.scale_mode = 0;
+    a.epilogue = epilogue;
+    a.cta_group = cta_group;
+    a.stream = static_cast<cudaStream_t>(stream);
+    if (ldy <= 0 || y_col_group_stride < 0) return kErrBadArgument;
+    return grouped_gemm_launch(a);
+}
+
+int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                     const int32_t* m_sizes, void* y, int M, int N, int K, int G, int64_t ldy,
+                                     int64_t y_col_group_stride, int cta_group, int32_t* status,
+                                     b200moe_stream_t stream) {
+    GGLaunch a{};
+    a.x = xq;
+    a.w = wq;
+    a.m_sizes = m_sizes;
+    a.y = y;
+    a.x_scale = x_scale;
+    a.w_scale = w_scale;
+    a.status = status;
+    a.ldy = ldy;
+    a.y_col_group_stride = y_col_group_stride;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.G = G;
+    a.elem_bytes = 1;
+    a.scale_mode = 1;
+    a.epilogue = 0;
+    a.cta_group = cta_group;
+    a.stream = static_cast<cudaStream_t>(stream);
+    if (ldy <= 0 || y_col_group_stride < 0) return kErrBadArgument;
+    return grouped_gemm_launch(a);
+}
+
+int b200moe_route_workspace_bytes(int R, int E, size_t* bytes) {
+    if (bytes == nullptr) return kErrBadArgument;
+    int chunk_len = 0, num_chunks = 0;
+    if (int e = route_plan(R, E, &chunk_len, &num_chunks)) return e;
+    *bytes = sizeof(int32_t) * static_cast<size_t>(num_chunks > 0 ? num_chunks : 1) * static_cast<size_t>(E);
+    return 0;
+}
+
+int b200moe_route(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
+                  int32_t* inv_perm, void* workspace, size_t workspace_bytes, int32_t* status,
+                  b200moe_stream_t stream) {
+    size_t need = 0;
+    if (int e = b200moe_route_workspace_bytes(R, E, &need)) return e;
+    if (m_sizes == nullptr || offsets == nullptr) return kErrBadArgument;
+    if (R > 0 && (ids == nullptr || perm == nullptr || inv_perm == nullptr || workspace == nullptr))
+        return kErrBadArgument;
+    if (R > 0 && workspace_bytes < need) return kErrTooLarge;
+    return route_launch(ids, R, E, m_sizes, offsets, perm, inv_perm, static_cast<int32_t*>(workspace), status,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_gather_rows(const void* src, const int32_t* idx, int div, void* dst, int rows, int64_t row_bytes,
+                        int src_rows, b200moe_stream_t stream) {
+    if (rows > 0 && (src == nullptr || idx == nullptr || dst == nullptr)) return kErrBadArgument;
+    return gather_rows_launch(src, idx, div, dst, rows, row_bytes, src_rows, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_swiglu(const void* in, void* out, int64_t rows, int d, b200moe_stream_t stream) {
+    if (rows > 0 && (in == nullptr || out == nullptr)) return kErrBadArgument;
+    return swiglu_launch(in, out, rows, d, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_combine_topk(const void* y, const int32_t* inv_perm, const float* weight, void* out, int T, int k,
+                         int H, int y_rows, b200moe_stream_t stream) {
+    if (T > 0 && (y == nullptr || inv_perm == nullptr || out == nullptr)) return kErrBadArgument;
+    return combine_topk_launch(y, inv_perm, weight, out, T, k, H, y_rows, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_quant_1x128(const void* x, int x_is_fp32, void* q, float* scales, int64_t rows, int K,
+                        b200moe_stream_t stream) {
+    if (rows > 0 && (x == nullptr || q == nullptr || scales == nullptr)) return kErrBadArgument;
+    return quant_1x128_launch(x, x_is_fp32, q, scales, rows, K, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

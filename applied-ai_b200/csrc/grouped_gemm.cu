@@ -1,0 +1,540 @@
+// Ragged ("grouped") GEMM for MoE experts on sm_100a:
+//     y[rows of group g, :] = x[rows of group g, :] @ w[g]^T
+// x is [M, K] row-major, w is [G, N, K] row-major (K-major operands for both), the
+// rows of x are partitioned into G consecutive groups by m_sizes[G] (device memory,
+// zeros allowed).  This replaces the persistent Triton kernels of the reference
+// (dev/triton_groupGEMM/groupgemm.py:131-254 bf16, :270-404 fp8 row-wise;
+// kernels/MoE/group_GEMM/triton/tgroup_gemm_forward.py:136-293, :311-482).
+//
+// Structure of one CTA (192 threads), persistent over output tiles:
+//   warp 0      TMA producer: fills a ring of shared-memory stages with a
+//               128-row box of x and this CTA's share of a 256-row box of w[g].
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (4 per stage) into one of
+//               two TMEM accumulators (256 fp32 columns each); tcgen05.commit
+//               releases stages and publishes finished accumulators.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, apply scales / SwiGLU,
+//               convert to bf16, store the valid rows and columns.
+// With CTAS == 2 two CTAs of a cluster form one 256x256 tile: each loads its own 128
+// rows of x and its own 128 rows of w[g], the leader issues cta_group::2 MMAs, and
+// both epilogues drain their own 128 accumulator rows.  No load is multicast.
+//
+// Tile order: groups in the order given; inside a group, row blocks vary fastest
+// within one 256-column panel of w[g], so tiles that run together share the panel.
+// Tile t of the global list belongs to cluster (t mod #clusters): static, no atomics,
+// so results are bit-identical from run to run.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b200moe_internal.h"
+#include "ptx.cuh"
+
+namespace b200moe {
+
+constexpr int kMaxGroups = 1024;
+constexpr int kRowsPerCta = 128;                    // accumulator rows (TMEM lanes) per CTA
+constexpr int kTileN = 256;                         // accumulator columns per tile
+constexpr int kRowBytes = 128;                      // one swizzle row: 64 bf16 or 128 e4m3 along K
+constexpr int kABytes = kRowsPerCta * kRowBytes;    // 16 KiB
+constexpr int kSubBoxBytes = 128 * kRowBytes;       // a 128-row box of w: 16 KiB
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr int kTmemCols = 2 * kTileN;               // two accumulators
+
+template <int CTAS>
+struct StageCfg {
+    static constexpr int kBBytes = (2 / CTAS) * kSubBoxBytes;  // this CTA's share of the w box
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = CTAS == 1 ? 4 : 6;
+    static constexpr int kRingBytes = kStages * kStageBytes;   // 192 KiB either way
+};
+
+struct SmemTail {
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    int invalid;
+    int total_tiles;
+    int row_off[kMaxGroups + 1];
+    int tile_off[kMaxGroups + 1];
+};
+
+template <int CTAS>
+constexpr size_t gg_smem_bytes() {
+    return 1024 + StageCfg<CTAS>::kRingBytes + sizeof(SmemTail);
+}
+
+__device__ __forceinline__ void report(int32_t* status, int code) {
+    if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+struct TileCoord {
+    int g, row0, row_end, n_idx;
+};
+
+// Maps a global tile number to its group and position.  `g` only moves forward.
+__device__ __forceinline__ TileCoord locate_tile(int t, int& g, const int* tile_off, const int* row_off,
+                                                 int tile_rows) {
+    while (tile_off[g + 1] <= t) ++g;
+    const int local = t - tile_off[g];
+    const int m_g = row_off[g + 1] - row_off[g];
+    const int tiles_m = (m_g + tile_rows - 1) / tile_rows;
+    TileCoord c;
+    c.g = g;
+    c.row0 = row_off[g] + (local % tiles_m) * tile_rows;
+    c.row_end = row_off[g + 1];
+    c.n_idx = local / tiles_m;
+    return c;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
+
+// ELEM_BYTES: 2 = bf16 operands, 1 = e4m3 operands.
+// SCALE: 0 none, 1 row-wise (x_scale[M], w_scale[G*N]).
+// EPI: 0 plain, 1 SwiGLU (w[g] = [gate rows 0..I) ; up rows I..2I), output has I columns).
+template <int ELEM_BYTES, int CTAS, int SCALE, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GGParams p) {
+#if defined(__CUDA_ARCH_FEAT_SM100_ALL)
+    using Cfg = StageCfg<CTAS>;
+    constexpr bool kFp8 = ELEM_BYTES == 1;
+    constexpr int kElemsPerStage = kRowBytes / ELEM_BYTES;  // K elements per stage
+    constexpr int kTileRows = kRowsPerCta * CTAS;
+    constexpr uint32_t kIdesc = make_idesc(kFp8, kTileRows, kTileN);
+    constexpr uint32_t kTxBytes = static_cast<uint32_t>(Cfg::kStageBytes) * CTAS;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t ring_addr = (raw_addr + 1023u) & ~1023u;
+    uint8_t* ring = smem_raw + (ring_addr - raw_addr);
+    SmemTail* st = reinterpret_cast<SmemTail*>(ring + Cfg::kRingBytes);
+    volatile int* abort_flag = &st->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = CTAS == 1 ? 0u : cluster_ctarank();
+    const int cluster_id = blockIdx.x / CTAS;
+    const int num_clusters = gridDim.x / CTAS;
+
+    // ---- prologue: group tables, barriers, TMEM
+    if (threadIdx.x == 0) {
+        st->abort_flag = 0;
+        st->invalid = 0;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // Exclusive prefix sums of rows and tiles over the groups, 32 groups per step.
+        int row_carry = 0, tile_carry = 0, bad = 0;
+        for (int base = 0; base < p.G; base += 32) {
+            const int g = base + lane;
+            int m = g < p.G ? p.m_sizes[g] : 0;
+            if (m < 0) {
+                bad = 1;
+                m = 0;
+            }
+            int tiles = ((m + kTileRows - 1) / kTileRows) * p.n_tiles;
+            int rs = m, ts = tiles;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int r2 = __shfl_up_sync(0xffffffffu, rs, d);
+                const int t2 = __shfl_up_sync(0xffffffffu, ts, d);
+                if (lane >= d) {
+                    rs += r2;
+                    ts += t2;
+                }
+            }
+            if (g < p.G) {
+                st->row_off[g] = row_carry + rs - m;
+                st->tile_off[g] = tile_carry + ts - tiles;
+            }
+            row_carry += __shfl_sync(0xffffffffu, rs, 31);
+            tile_carry += __shfl_sync(0xffffffffu, ts, 31);
+            if (row_carry > p.M) bad = 1;  // also stops int overflow of the running sum
+        }
+        bad = __any_sync(0xffffffffu, bad);
+        if (lane == 0) {
+            st->row_off[p.G] = row_carry;
+            st->tile_off[p.G] = tile_carry;
+            st->total_tiles = bad ? 0 : tile_carry;
+            st->invalid = bad;
+            if (bad) report(p.status, kStatusBadGroupSizes);
+            for (int s = 0; s < Cfg::kStages; ++s) {
+                mbar_init(&st->full[s], 1);
+                mbar_init(&st->empty[s], 1);
+            }
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&st->acc_full[b], 1);
+                mbar_init(&st->acc_empty[b], kEpiWarps * CTAS);
+            }
+            mbar_init_fence();
+            prefetch_tensormap(&tm_x);
+            prefetch_tensormap(&tm_w);
+        }
+    } else if (warp == 1) {
+        tmem_alloc<CTAS>(&st->tmem_base, kTmemCols);
+        tmem_relinquish<CTAS>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();  // peer barriers exist before anything signals them
+    tc_fence_after();
+
+    const uint32_t tmem_base = st->tmem_base;
+    const int total_tiles = st->total_tiles;
+    const int num_kb = (p.K + kElemsPerStage - 1) / kElemsPerStage;
+
+    if (warp == 0) {
+        // ================= TMA producer (one thread per CTA)
+        if (lane == 0) {
+            int g = 0, stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
+                const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
+                const int row0 = tc.row0 + static_cast<int>(cta_rank) * kRowsPerCta;
+                // Rows of w[g] for the two 128-row boxes of this tile.
+                const int nb0 = EPI == 1 ? tc.n_idx * 128 : tc.n_idx * kTileN;
+                const int nb1 = EPI == 1 ? p.n_out + tc.n_idx * 128 : tc.n_idx * kTileN + 128;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag)) {
+                        report(p.status, kStatusTimeoutProducer);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = ring_addr + stage * Cfg::kStageBytes;
+                    const uint32_t b_dst = a_dst + kABytes;
+                    const int k0 = kb * kElemsPerStage;
+                    if constexpr (CTAS == 1) {
+                        const uint32_t bar = smem_u32(&st->full[stage]);
+                        mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                        tma_load_2d(&tm_x, bar, a_dst, k0, row0);
+                        tma_load_3d(&tm_w, bar, b_dst, k0, nb0, tc.g);
+                        tma_load_3d(&tm_w, bar, b_dst + kSubBoxBytes, k0, nb1, tc.g);
+                    } else {
+                        // Bytes of both CTAs are counted on the leader's barrier.
+                        const uint32_t bar = mapa_shared(smem_u32(&st->full[stage]), 0);
+                        if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                        tma_load_2d_pair(&tm_x, bar, a_dst, k0, row0);
+                        tma_load_3d_pair(&tm_w, bar, b_dst, k0, cta_rank == 0 ? nb0 : nb1, tc.g);
+                    }
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer (one thread of the leader CTA)
+        if (lane == 0 && cta_rank == 0) {
+            int stage = 0, buf = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
+                if (!mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
+                    report(p.status, kStatusTimeoutMmaAcc);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kTileN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&st->full[stage], phase, abort_flag)) {
+                        report(p.status, kStatusTimeoutMmaFull);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = ring_addr + stage * Cfg::kStageBytes;
+                    const uint64_t a_desc = make_sw128_kmajor_desc(a_addr);
+                    const uint64_t b_desc = make_sw128_kmajor_desc(a_addr + kABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // 32 bytes along K per MMA: +2 in the descriptor's 16-byte units.
+                        umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc,
+                                         (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit<CTAS>(&st->empty[stage]);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit<CTAS>(&st->acc_full[buf]);
+                buf ^= 1;
+                if (buf == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ================= epilogue (4 warps; warp w owns TMEM lanes 32*(w%4)..+31)
+        const int quarter = warp & 3;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t acc_empty_leader =
+            CTAS == 1 ? smem_u32(&st->acc_empty[0]) : mapa_shared(smem_u32(&st->acc_empty[0]), 0);
+        __nv_bfloat16* const y = static_cast<__nv_bfloat16*>(p.y);
+        int g = 0, buf = 0;
+        uint32_t acc_phase = 0;
+        for (int t = cluster_id; t < total_tiles; t += num_clusters) {
+            const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(&st->acc_full[buf], acc_phase, abort_flag) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) report(p.status, kStatusTimeoutEpilogue);
+                break;
+            }
+            tc_fence_after();
+            const int row = tc.row0 + static_cast<int>(cta_rank) * kRowsPerCta + quarter * 32 + lane;
+            const bool row_ok = row < tc.row_end;
+            const uint32_t t_acc = tmem_base + lane_base + static_cast<uint32_t>(buf * kTileN);
+            float x_scale = 1.0f;
+            if constexpr (SCALE == 1) x_scale = row_ok ? p.x_scale[row] : 0.0f;
+
+            constexpr int kOutCols = EPI == 1 ? 128 : kTileN;  // output columns per tile
+            const int col0 = tc.n_idx * kOutCols;              // first output column of the tile (within group)
+            __nv_bfloat16* const y_row =
+                y + static_cast<size_t>(row_ok ? row : 0) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
+            const float* const w_scale_g = SCALE == 1 ? p.w_scale + static_cast<size_t>(tc.g) * p.N : nullptr;
+
+#pragma unroll 1
+            for (int c = 0; c < kOutCols / 32; ++c) {
+                const int col = col0 + c * 32;
+                if (col >= p.n_out) break;  // warp-uniform: nothing left to store in this tile
+                uint32_t v[32];
+                float f[32];
+                tmem_ld_32x32(t_acc + static_cast<uint32_t>(c * 32), v);
+                if constexpr (EPI == 1) {
+                    uint32_t u[32];
+                    tmem_ld_32x32(t_acc + static_cast<uint32_t>(128 + c * 32), u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j]));
+                } else {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                }
+                if constexpr (SCALE == 1) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int cj = col + j;
+                        const float ws = cj < p.n_out ? __ldg(w_scale_g + cj) : 0.0f;
+                        f[j] = f[j] * x_scale * ws;
+                    }
+                }
+                if (row_ok) {
+                    __nv_bfloat16* dst = y_row + col;
+                    const bool vec = (col + 32 <= p.n_out) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+                    if (vec) {
+                        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 o;
+                            o.x = pack_bf16x2(f[q * 8 + 0], f[q * 8 + 1]);
+                            o.y = pack_bf16x2(f[q * 8 + 2], f[q * 8 + 3]);
+                            o.z = pack_bf16x2(f[q * 8 + 4], f[q * 8 + 5]);
+                            o.w = pack_bf16x2(f[q * 8 + 6], f[q * 8 + 7]);
+                            d4[q] = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < p.n_out) dst[j] = __float2bfloat16_rn(f[j]);
+                    }
+                }
+            }
+            // Accumulator drained: hand it back to the MMA issuer.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
+            buf ^= 1;
+            if (buf == 0) acc_phase ^= 1u;
+        }
+    }
+
+    // ---- teardown: everyone meets, then the allocating warp frees TMEM
+    __syncwarp();
+    if (*abort_flag) {
+        // A wait gave up.  Give copies already issued time to land before the CTA exits.
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();  // the peer may still read this CTA's shared memory until here
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<CTAS>(tmem_base, kTmemCols);
+    }
+#else
+    if (threadIdx.x == 0 && blockIdx.x == 0) report(p.status, kStatusWrongArch);
+#endif
+}
+
+// ------------------------------------------------------------------ host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so the library links against the
+// CUDA runtime only.
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// x viewed as [rows, K]; box = 128 rows x 128 bytes, 128-byte swizzle.
+static int encode_x_map(CUtensorMap* m, const void* x, int rows, int K, int elem_bytes) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return kErrNoDriverEntry;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * elem_bytes};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                     const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
+}
+
+// w viewed as [G, rows_per_group, K]; box = 1 group x 128 rows x 128 bytes.  The group
+// is its own dimension so a box that runs past a group's last row is zero-filled
+// instead of reading the next expert's weights.
+static int encode_w_map(CUtensorMap* m, const void* w, int G, int rows_per_group, int K, int elem_bytes) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return kErrNoDriverEntry;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows_per_group),
+                          static_cast<cuuint64_t>(G)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(K) * elem_bytes,
+                             static_cast<cuuint64_t>(K) * elem_bytes * rows_per_group};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                     const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    int cc_major = 0, cc_minor = 0;
+};
+static int get_device_info(DeviceInfo* out) {
+    static thread_local int cached_dev = -1;
+    static thread_local DeviceInfo cached;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev != cached_dev) {
+        cudaDeviceProp prop;
+        e = cudaGetDeviceProperties(&prop, dev);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        cached.sms = prop.multiProcessorCount;
+        cached.cc_major = prop.major;
+        cached.cc_minor = prop.minor;
+        cached_dev = dev;
+    }
+    *out = cached;
+    return 0;
+}
+
+template <int ELEM_BYTES, int CTAS, int SCALE, int EPI>
+static int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const GGParams& p, int sms,
+                          cudaStream_t stream) {
+    auto kernel = gg_kernel<ELEM_BYTES, CTAS, SCALE, EPI>;
+    constexpr size_t smem = gg_smem_bytes<CTAS>();
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured_dev = dev;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>((sms / CTAS) * CTAS), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, p);
+    return static_cast<int>(e);
+}
+
+int grouped_gemm_launch(const GGLaunch& a) {
+    if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0 || a.x == nullptr || a.w == nullptr || a.y == nullptr ||
+        a.m_sizes == nullptr)
+        return kErrBadArgument;
+    if (a.G > kMaxGroups) return kErrTooManyGroups;
+    if (a.elem_bytes != 1 && a.elem_bytes != 2) return kErrBadArgument;
+    if ((static_cast<long long>(a.K) * a.elem_bytes) % 16 != 0) return kErrAlignment;  // TMA row pitch
+    if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.w) & 15u)) return kErrAlignment;
+    if (a.scale_mode == 1 && (a.x_scale == nullptr || a.w_scale == nullptr)) return kErrBadArgument;
+    if (a.scale_mode != 0 && a.scale_mode != 1) return kErrBadArgument;
+    if (a.epilogue == 1 && (a.N % 2 != 0)) return kErrBadArgument;
+    if (a.epilogue != 0 && a.epilogue != 1) return kErrBadArgument;
+    if (a.epilogue == 1 && a.scale_mode != 0) return kErrBadArgument;
+    if (a.M == 0) return 0;
+
+    DeviceInfo di;
+    if (int e = get_device_info(&di)) return e;
+    if (di.cc_major != 10) return kErrWrongDevice;
+
+    CUtensorMap tm_x, tm_w;
+    if (int e = encode_x_map(&tm_x, a.x, a.M, a.K, a.elem_bytes)) return e;
+    if (int e = encode_w_map(&tm_w, a.w, a.G, a.N, a.K, a.elem_bytes)) return e;
+
+    GGParams p;
+    p.m_sizes = a.m_sizes;
+    p.y = a.y;
+    p.x_scale = a.x_scale;
+    p.w_scale = a.w_scale;
+    p.status = a.status;
+    p.M = a.M;
+    p.N = a.N;
+    p.K = a.K;
+    p.G = a.G;
+    p.ldy = a.ldy;
+    p.y_col_group_stride = a.y_col_group_stride;
+    p.n_out = a.epilogue == 1 ? a.N / 2 : a.N;
+    p.n_tiles = a.epilogue == 1 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;
+
+    const int ctas = a.cta_group == 1 ? 1 : 2;
+    const bool fp8 = a.elem_bytes == 1;
+#define B200MOE_LAUNCH(EB, SC, EP)                                                          \
+    (ctas == 1 ? launch_variant<EB, 1, SC, EP>(tm_x, tm_w, p, di.sms, a.stream)              \
+               : launch_variant<EB, 2, SC, EP>(tm_x, tm_w, p, di.sms, a.stream))
+    if (!fp8 && a.epilogue == 0) return B200MOE_LAUNCH(2, 0, 0);
+    if (!fp8 && a.epilogue == 1) return B200MOE_LAUNCH(2, 0, 1);
+    if (fp8 && a.scale_mode == 1) return B200MOE_LAUNCH(1, 1, 0);
+    if (fp8 && a.scale_mode == 0 && a.epilogue == 0) return B200MOE_LAUNCH(1, 0, 0);
+#undef B200MOE_LAUNCH
+    return kErrBadArgument;
+}
+
+}  // namespace b200moe

@@ -1,0 +1,23 @@
+// Launchers of the memory-bound MoE helper kernels (internal to libb200moe.so).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200moe {
+
+constexpr int kRouteMaxExperts = 4096;
+constexpr int kRouteMaxChunks = 1024;
+
+// Splits R ids into chunks for the routing kernels; scratch needed = num_chunks * E int32.
+int route_plan(int R, int E, int* chunk_len, int* num_chunks);
+int route_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
+                 int32_t* inv_perm, int32_t* counts, int32_t* status, cudaStream_t stream);
+int gather_rows_launch(const void* src, const int32_t* idx, int div, void* dst, int rows, long long row_bytes,
+                       int src_rows, cudaStream_t stream);
+int swiglu_launch(const void* in, void* out, long long rows, int d, cudaStream_t stream);
+int combine_topk_launch(const void* y, const int32_t* inv_perm, const float* weight, void* out, int T, int k, int H,
+                        int y_rows, cudaStream_t stream);
+int quant_1x128_launch(const void* x, int x_is_fp32, void* q, float* scales, long long rows, int K,
+                       cudaStream_t stream);
+
+}  // namespace b200moe

@@ -1,0 +1,147 @@
+"""Grouped GEMM entry points with the reference's call surface.
+
+    grouped_gemm(x, w, m_sizes)                                  -> y [M, N]
+    grouped_gemm_fp8_rowwise(x, w, m_sizes, x_scale, w_scale)    -> y [M, N]
+
+mirror dev/triton_groupGEMM/groupgemm.py:518-531 (wrapper `_grouped_gemm` :407-515):
+x [M, K] and w [G*N, K] (or [G, N, K]) contiguous, m_sizes [G] int32 on the device,
+output freshly allocated bf16.  `grouped_gemm_forward` (the [M, N*G] block layout of
+kernels/MoE/group_GEMM/triton/tgroup_gemm_forward.py:626) is in tgroup_gemm_forward.py.
+
+Torch is only the host here (memory, streams); the arithmetic runs in libb200moe.so.
+Errors follow what the reference's tests expect (dev/triton_groupGEMM/testing/
+unit_tests.py:168-212): RuntimeError for shape/dtype/contiguity problems, ValueError
+for a group count that does not fit `w`, ValueError for group sizes the device
+rejects (negative, or adding up to more rows than x has).
+"""
+import torch
+
+from . import _lib
+
+_default_check = True
+_status_words = {}
+
+
+def set_default_check(flag):
+    """With checking on (the default) every call reads back a 4-byte status word after
+    the launch (one synchronisation) and raises on bad group sizes.  Turn it off for
+    benchmarking or when m_sizes is known to be valid."""
+    global _default_check
+    _default_check = bool(flag)
+
+
+def _status_word(device):
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    word = _status_words.get(key)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = word
+    return word
+
+
+def raise_on_status(word, what):
+    """Read the device status word; if set, clear it and raise."""
+    code = int(word.item())
+    if code == 0:
+        return
+    word.zero_()
+    msg = f"{what}: {_lib.describe_status(code)} (status {code})"
+    if code == 1:
+        raise ValueError(msg)
+    raise _lib.B200MoeError(msg)
+
+
+def _require(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _prepare(x, w, m_sizes, elem_dtype):
+    _require(isinstance(x, torch.Tensor) and isinstance(w, torch.Tensor) and isinstance(m_sizes, torch.Tensor),
+             "x, w and m_sizes must be tensors")
+    _require(x.is_cuda and w.is_cuda and m_sizes.is_cuda, "x, w and m_sizes must be CUDA tensors (no CPU path)")
+    _require(x.device == w.device == m_sizes.device, "x, w and m_sizes must be on the same device")
+    _require(x.dim() == 2, "x must be [M, K]")
+    _require(w.dim() in (2, 3), "w must be [G*N, K] or [G, N, K]")
+    _require(m_sizes.dim() == 1 and m_sizes.numel() > 0, "m_sizes must be a non-empty 1-D tensor")
+    _require(x.is_contiguous() and w.is_contiguous() and m_sizes.is_contiguous(),
+             "x, w and m_sizes must be contiguous")
+    _require(x.dtype == elem_dtype and w.dtype == elem_dtype, f"x and w must be {elem_dtype}")
+    _require(m_sizes.dtype in (torch.int32, torch.int64), "m_sizes must be int32")
+    if m_sizes.dtype != torch.int32:
+        m_sizes = m_sizes.to(torch.int32)
+    G = m_sizes.shape[0]
+    M, K = x.shape
+    _require(K == w.shape[-1], f"K mismatch: x has {K} columns, w has {w.shape[-1]}")
+    if w.dim() == 3:
+        if w.shape[0] != G:
+            raise ValueError(f"m_sizes has {G} groups but w has {w.shape[0]}")
+        N = w.shape[1]
+    else:
+        if w.shape[0] % G != 0:
+            raise ValueError(f"w has {w.shape[0]} rows, not a multiple of the {G} groups in m_sizes")
+        N = w.shape[0] // G
+    _require(N > 0 and K > 0, "N and K must be positive")
+    _require((K * x.element_size()) % 16 == 0, "K * element size must be a multiple of 16 bytes (TMA row pitch)")
+    return m_sizes, G, M, N, K
+
+
+def _launch_bf16(x, w, m_sizes, y, M, N, K, G, ldy, col_stride, epilogue, cta_group, check, what):
+    lib = _lib.load()
+    word = _status_word(x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200moe_grouped_gemm_bf16(x.data_ptr(), w.data_ptr(), m_sizes.data_ptr(), y.data_ptr(), M, N, K, G,
+                                           ldy, col_stride, epilogue, cta_group, word.data_ptr(), stream)
+    _lib.check(rc, what)
+    if _default_check if check is None else check:
+        raise_on_status(word, what)
+
+
+def grouped_gemm(x, w, m_sizes, *, epilogue="none", cta_group=0, check=None):
+    """y[rows of group g] = x[rows of group g] @ w[g].T, bf16 in, fp32 accumulate, bf16 out.
+
+    epilogue="swiglu": w[g] is [gate; up] (N = 2*I rows) and y gets I columns,
+    silu(gate) * up computed on the fp32 accumulators.
+    """
+    m_sizes, G, M, N, K = _prepare(x, w, m_sizes, torch.bfloat16)
+    epi = {"none": 0, "swiglu": 1}.get(epilogue)
+    _require(epi is not None, "epilogue must be 'none' or 'swiglu'")
+    if epi == 1:
+        _require(N % 2 == 0, "SwiGLU needs an even number of weight rows per group")
+    n_out = N // 2 if epi == 1 else N
+    y = torch.empty((M, n_out), device=x.device, dtype=torch.bfloat16)
+    if M > 0:
+        _launch_bf16(x, w, m_sizes, y, M, N, K, G, n_out, 0, epi, cta_group, check, "grouped_gemm")
+    return y
+
+
+def _prepare_scales(x_scale, w_scale, M, G, N, device):
+    _require(isinstance(x_scale, torch.Tensor) and isinstance(w_scale, torch.Tensor), "scales must be tensors")
+    _require(x_scale.device == device and w_scale.device == device, "scales must be on the same device as x")
+    _require(x_scale.dtype == torch.float32 and w_scale.dtype == torch.float32, "scales must be float32")
+    _require(x_scale.is_contiguous() and w_scale.is_contiguous(), "scales must be contiguous")
+    _require(x_scale.numel() == M, f"x_scale must have M={M} entries")
+    _require(w_scale.numel() == G * N, f"w_scale must have G*N={G * N} entries")
+
+
+def grouped_gemm_fp8_rowwise(x, w, m_sizes, x_scale, w_scale, *, cta_group=0, check=None):
+    """(xq @ wq[g].T) * x_scale[:, None] * w_scale[None, g*N:(g+1)*N] -> bf16 [M, N].
+
+    x, w are float8_e4m3fn; x_scale [M] and w_scale [G*N] are fp32."""
+    m_sizes, G, M, N, K = _prepare(x, w, m_sizes, torch.float8_e4m3fn)
+    _prepare_scales(x_scale, w_scale, M, G, N, x.device)
+    y = torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+    if M == 0:
+        return y
+    lib = _lib.load()
+    word = _status_word(x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200moe_grouped_gemm_fp8_rowwise(x.data_ptr(), w.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
+                                                  m_sizes.data_ptr(), y.data_ptr(), M, N, K, G, N, 0, cta_group,
+                                                  word.data_ptr(), stream)
+    _lib.check(rc, "grouped_gemm_fp8_rowwise")
+    if _default_check if check is None else check:
+        raise_on_status(word, "grouped_gemm_fp8_rowwise")
+    return y

@@ -1,0 +1,330 @@
+"""Benchmark of the MoE grouped-GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5|c3]
+
+Default workload ("c2"): bf16 grouped GEMM at the DeepSeek-V3 routed-expert gate+up
+shape — G=8 experts, K=7168, N=4096, 16384 rows, group sizes multiples of 128, seeded
+synthetic data.  One step = one grouped GEMM over the whole batch.  Metric: TFLOPS
+(2*M*N*K / time).  With N > 1 GPUs every rank holds its own 8 experts and 16384 rows
+(expert-sharded, no exchange in this path) and the value is the sum over ranks.
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the reference's own ground
+truth for this path — the torch per-expert matmul loop on the host CPU cores — on a
+bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (G, M, N, K)
+    "c2": (8, 16384, 4096, 7168),
+    "c5": (128, 8192, 1408, 2048),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        d = json.load(open(path))
+        return {"bf16_tflops": float(d["bf16_tflops"]), "bf16_tflops_sustained": float(d["bf16_tflops_sustained"]),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    except Exception:
+        return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.thread = [], None, None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [r for r in self.rows if t0 - 0.05 <= r[0] <= t1 + 0.05] or self.rows
+        for _, line in rows:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def cpu_loop_tflops(G, N, K, rows_per_group, repeats, seed=1001):
+    """The reference's per-expert loop (dev/triton_groupGEMM/testing/base_testing.py:125-131)
+    in fp32 on the host cores, over `rows_per_group` rows of each group."""
+    from oracle import grouped as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(seed)
+    M = G * rows_per_group
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(G, N, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+    m_sizes = torch.full((G,), rows_per_group, dtype=torch.int32)
+    xf, wf = x.float(), w.float()
+    O.grouped_gemm_ref(xf[: G * 8], wf, torch.full((G,), 8, dtype=torch.int32))  # touch pages, spin up threads
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        O.grouped_gemm_ref(xf, wf, m_sizes)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    t = times[len(times) // 2]
+    return 2.0 * M * N * K / t / 1e12, t, M
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    G, M, N, K = WORKLOADS[args.workload]
+    rows = 256 if args.workload == "c2" else max(8, M // G)
+    torch.set_num_threads(os.cpu_count() or 1)
+    from oracle import grouped as O
+    g = torch.Generator().manual_seed(1001)
+    Ms = G * rows
+    x = torch.randn(Ms, K, generator=g).to(torch.bfloat16).float()
+    w = (torch.randn(G, N, K, generator=g) * K ** -0.5).to(torch.bfloat16).float()
+    m_sizes = torch.full((G,), rows, dtype=torch.int32)
+    for _ in range(max(1, min(args.warmup, 3))):
+        O.grouped_gemm_ref(x, w, m_sizes)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.grouped_gemm_ref(x, w, m_sizes)
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 2.0 * Ms * N * K / dt / 1e12
+    sample = f"{rows} rows of each of the {G} groups ({Ms} of {M} rows), full N and K, fp32 torch.matmul loop"
+    line = {
+        "impl": "reference", "metric": "grouped_gemm_tflops", "value": tflops, "unit": "TFLOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: grouped GEMM G={G} K={K} N={N} M={M}", "sampled_rows": Ms},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOPS", "cores": torch.get_num_threads(), "kind": "reference",
+                         "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import applied_ai_b200 as B
+    from applied_ai_b200 import _lib, configs
+
+    rank, world, local = dist_env()
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load(build_if_missing=False)
+    B.set_default_check(False)
+
+    G, M, N, K = WORKLOADS[args.workload]
+    seed = 1001 + 17 * rank
+    if args.workload == "c2":
+        x, w, m_sizes = configs.c2_deepseek_gate_up(seed=seed, device=dev)
+    else:
+        x, w, m_sizes = configs.c5_skew(seed=1004 + 17 * rank, device=dev)
+    rows = int(m_sizes.sum())
+    flops = 2.0 * rows * N * K
+    input_bytes = x.numel() * 2 + w.numel() * 2 + rows * N * 2
+
+    def step():
+        return B.grouped_gemm(x, w, m_sizes, cta_group=args.cta_group)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    y = step()
+    torch.cuda.synchronize()
+    status = int(B.groupgemm._status_word(dev).item())
+    assert status == 0, f"device status {status}"
+
+    # correctness guard on the timed configuration: a sample of rows against the host loop
+    if rank == 0:
+        from oracle import grouped as O
+        gsel = torch.Generator().manual_seed(7)
+        start, worst = 0, 0.0
+        ms = m_sizes.cpu()
+        for e in range(G):
+            mg = int(ms[e])
+            if mg:
+                pick = start + torch.randint(0, mg, (2,), generator=gsel)
+                ref = x[pick.to(dev)].cpu().float() @ w[e].cpu().float().T
+                worst = max(worst, O.rel_err(y[pick.to(dev)].cpu().float(), ref))
+            start += mg
+        assert worst <= 1e-2, f"bench output fails parity: {worst}"
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    t_wall1 = time.time()
+    ms_total = ev0.elapsed_time(ev1)
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+
+    # end to end: pinned host activations -> device, grouped GEMM through the public API, result -> host
+    x_host = x.cpu().pin_memory()
+    m_host = m_sizes.cpu().pin_memory()
+    y_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty_like(x)
+    m_dev = torch.empty_like(m_sizes)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        m_dev.copy_(m_host, non_blocking=True)
+        out = B.grouped_gemm(x_dev, w, m_dev, cta_group=args.cta_group)
+        y_host.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / e2e_steps
+
+    t = torch.tensor([ms_total, ms_e2e, flops], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms_total, ms_e2e, flops_all = float(tmax[0]), float(tmax[1]), float(tsum[2])
+    else:
+        flops_all = flops
+    ms_step = ms_total / args.steps
+
+    if rank == 0:
+        peaks = load_peaks()
+        tflops = flops_all / (ms_step * 1e-3) / 1e12
+        per_gpu = flops / (ms_step * 1e-3) / 1e12
+        if args.workload == "c2":
+            roof = {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": per_gpu / peaks["bf16_tflops"], "traffic": args.traffic,
+                    "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
+                    "frac_of_sustained": per_gpu / peaks["bf16_tflops_sustained"]}
+        else:
+            nonempty = int((m_sizes > 0).sum())
+            alg_bytes = rows * K * 2 + nonempty * N * K * 2 + rows * N * 2
+            gbs = alg_bytes / (ms_step * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": gbs / peaks["hbm_gbs"], "traffic": args.traffic, "peak_source": peaks["source"]}
+        cpu_rows = 1024 if args.workload == "c2" else max(8, M // G)
+        cpu_tf, cpu_t, cpu_M = cpu_loop_tflops(G, N, K, cpu_rows, repeats=3)
+        line = {
+            "metric": "grouped_gemm_tflops", "value": tflops, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: grouped GEMM G={G} K={K} N={N} M={M} per GPU, "
+                                   "m_sizes multinomial" + (" x128" if args.workload == "c2" else " Zipf(1.2)"),
+                       "cta_group": args.cta_group or "auto", "l2": f"inputs {input_bytes >> 20} MiB per step > 126 MiB L2",
+                       "sharding": "experts across ranks, no exchange" if world > 1 else "single GPU"},
+            "roofline": roof,
+            "cpu_baseline": {"value": cpu_tf, "unit": "TFLOPS", "cores": torch.get_num_threads(), "kind": "reference",
+                             "sample": f"{cpu_rows} rows per group ({cpu_M} of {M} rows), fp32 torch per-expert loop, "
+                                       f"median of 3, {cpu_t:.2f} s each"},
+            "e2e": {"value": flops_all / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOPS",
+                    "h2d_bytes_per_step": x.numel() * 2 + G * 4, "d2h_bytes_per_step": M * N * 2,
+                    "ms_per_step": ms_e2e, "note": "activations and m_sizes from pinned host memory, weights resident"},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--cta-group", type=int, default=0, dest="cta_group")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per launch from an ncu capture, echoed into the roofline object")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,109 @@
+/* libb200moe.so — C ABI of the B200 (sm_100a) MoE grouped-GEMM engine.
+ *
+ * Every entry point takes raw DEVICE pointers, plain integers and a CUDA stream
+ * (a cudaStream_t passed as void*; NULL = the default stream), enqueues its work on
+ * that stream and returns without synchronising.  Nothing here allocates device
+ * memory.  The device that owns the pointers must be current on the calling thread.
+ *
+ * Return value: 0 = enqueued; > 0 = a cudaError_t from the runtime; < 0 = one of
+ * the B200MOE_E* codes below.  Entry points never throw and never abort.
+ *
+ * `status` (optional, may be NULL) points to one zero-initialised int32 in device
+ * memory.  A kernel that meets bad data or gives up a bounded wait writes a non-zero
+ * B200MOE_S* code there (first writer wins) and does no further work; the caller reads
+ * it after synchronising.  The word is never reset by the library.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* b200moe_stream_t;
+
+/* negative return codes */
+#define B200MOE_EBADARG (-1)       /* null pointer, non-positive size, unknown mode */
+#define B200MOE_EALIGN (-2)        /* pointer not 16-byte aligned, or K * element size not a multiple of 16 */
+#define B200MOE_ETOOMANYGROUPS (-3) /* G > 1024 */
+#define B200MOE_ENODRIVER (-4)     /* cuTensorMapEncodeTiled could not be resolved */
+#define B200MOE_ETENSORMAP (-5)    /* the driver rejected a tensor map */
+#define B200MOE_EWRONGDEVICE (-6)  /* current device is not compute capability 10.x */
+#define B200MOE_ETOOLARGE (-7)     /* workspace too small / size beyond a stated maximum */
+
+/* device status word */
+#define B200MOE_SBADSIZES 1        /* negative m_sizes entry, sum(m_sizes) > M, or an expert id outside [0, E) */
+#define B200MOE_STIMEOUT_FIRST 16  /* 16..19: a bounded wait inside the GEMM kernel ran out */
+#define B200MOE_STIMEOUT_LAST 19
+#define B200MOE_SWRONGARCH 32
+
+/* flags of the grouped GEMM entry points */
+#define B200MOE_EPI_NONE 0
+#define B200MOE_EPI_SWIGLU 1  /* w[g] = [gate rows 0..N/2) ; up rows N/2..N); y gets N/2 columns: silu(gate)*up */
+#define B200MOE_CTA_AUTO 0    /* 1 = one CTA per 128x256 tile, 2 = a CTA pair per 256x256 tile */
+
+int b200moe_version(void);
+
+/* y[rows of group g, g*y_col_group_stride + (0..N)] = x[rows of group g, :] @ w[g]^T
+ * x [M,K] bf16 row-major, w [G,N,K] bf16 row-major, m_sizes [G] int32 (device; zeros
+ * allowed; sum <= M, trailing rows of y are then left untouched), y bf16 with `ldy`
+ * elements between rows.  fp32 accumulation, one rounding to bf16.
+ * y_col_group_stride = 0, ldy = N gives the [M,N] layout of
+ *   grouped_gemm(x, w, m_sizes)            dev/triton_groupGEMM/groupgemm.py:518 (-> :407);
+ * y_col_group_stride = N, ldy = N*G gives the [M, N*G] block layout of
+ *   grouped_gemm_forward(x, w, m_sizes)    kernels/MoE/group_GEMM/triton/tgroup_gemm_forward.py:626 (-> :485).
+ * With B200MOE_EPI_SWIGLU the activation of v0_moe_fused.py:284 (silu_and_mul) is
+ * applied to the accumulators and y has N/2 columns per group. */
+int b200moe_grouped_gemm_bf16(const void* x, const void* w, const int32_t* m_sizes, void* y, int M, int N, int K,
+                              int G, int64_t ldy, int64_t y_col_group_stride, int epilogue, int cta_group,
+                              int32_t* status, b200moe_stream_t stream);
+
+/* Row-wise scaled FP8: y = (xq @ wq[g]^T) * x_scale[row] * w_scale[g*N + col].
+ * xq [M,K], wq [G,N,K] float8_e4m3fn; x_scale [M] fp32; w_scale [G*N] fp32; y bf16.
+ * Replaces grouped_gemm_fp8_rowwise(x, w, m_sizes, x_scale, w_scale)
+ *   dev/triton_groupGEMM/groupgemm.py:524, kernels/MoE/group_GEMM/triton/tgroup_gemm_forward.py:632. */
+int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                     const int32_t* m_sizes, void* y, int M, int N, int K, int G, int64_t ldy,
+                                     int64_t y_col_group_stride, int cta_group, int32_t* status,
+                                     b200moe_stream_t stream);
+
+/* Routing: stable counting sort of ids[R] (R = tokens*top_k, flat index t*top_k + j)
+ * by expert.  m_sizes[E], offsets[E+1], perm[R] (sorted position -> flat index),
+ * inv_perm[R] (flat index -> sorted position, -1 for an id outside [0,E)).
+ * Takes the place of vLLM's moe_align_block_size as called at
+ * kernels/triton/inference/col_major_moe_gemm/v0_moe_fused.py:138-180, without the
+ * padding (the GEMM handles ragged groups).  `workspace` is scratch of at least
+ * b200moe_route_workspace_bytes(R, E) bytes. */
+int b200moe_route_workspace_bytes(int R, int E, size_t* bytes);
+int b200moe_route(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
+                  int32_t* inv_perm, void* workspace, size_t workspace_bytes, int32_t* status,
+                  b200moe_stream_t stream);
+
+/* dst[p, :] = src[idx[p] / div, :] for p < rows; row_bytes bytes per row.  The
+ * indexed load the reference's GEMM does per tile (v0_moe_fused.py:95, offs_token //
+ * top_k), as one pass.  Entries with idx < 0 or a source row >= src_rows are skipped. */
+int b200moe_gather_rows(const void* src, const int32_t* idx, int div, void* dst, int rows, int64_t row_bytes,
+                        int src_rows, b200moe_stream_t stream);
+
+/* out[r, 0..d) = silu(in[r, 0..d)) * in[r, d..2d), bf16 (ops.silu_and_mul, v0_moe_fused.py:284). */
+int b200moe_swiglu(const void* in, void* out, int64_t rows, int d, b200moe_stream_t stream);
+
+/* out[t, :] = sum_j weight[t,j] * y[inv_perm[t*k+j], :]  (bf16 in/out, fp32 sum in
+ * ascending j; weight may be NULL = 1).  The routed-weight multiply and torch.sum of
+ * v0_moe_fused.py:122-126, :291-296. */
+int b200moe_combine_topk(const void* y, const int32_t* inv_perm, const float* weight, void* out, int T, int k,
+                         int H, int y_rows, b200moe_stream_t stream);
+
+/* 1x128 e4m3 quantiser: scale = max(amax,1e-12)/448, q = clamp(x/scale, +-448).
+ * x [rows,K] bf16 (x_is_fp32 = 0) or fp32 (1); q [rows,K] e4m3; scales [rows,K/128].
+ * float8_groupwise_quantize, kernels/triton/inference/fp8/float8_groupwise_quant.py:53. */
+int b200moe_quant_1x128(const void* x, int x_is_fp32, void* q, float* scales, int64_t rows, int K,
+                        b200moe_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

@@ -1,0 +1,111 @@
+"""Routing, gather, SwiGLU, combine, quantiser and the whole MoE layer on the GPU against
+the CPU oracle and the fixtures produced by the reference's code."""
+import numpy as np
+import pytest
+import torch
+
+import applied_ai_b200 as B
+from applied_ai_b200 import configs as C
+from oracle import grouped as O
+from tests.helpers import BF16_REL_TOL, bf16_from_bits, load_npz
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def check_route(ids, E):
+    m_sizes, offsets, perm, inv = B.route(ids.to(DEV), E)
+    rm, ro, rp, ri = O.route_ref(ids, E)
+    assert torch.equal(m_sizes.cpu(), rm) and torch.equal(offsets.cpu(), ro)
+    assert torch.equal(perm.cpu(), rp) and torch.equal(inv.cpu(), ri)
+    for t in (m_sizes, offsets, perm, inv):
+        assert t.dtype == torch.int32
+
+
+def test_route_bit_exact():
+    g = torch.Generator().manual_seed(1)
+    check_route(torch.tensor([[2, 3, 4], [1, 2, 4], [1, 3, 4], [1, 2, 3]], dtype=torch.int32), 5)  # docstring example
+    for (T, k, E) in [(1, 1, 1), (7, 2, 8), (4096, 2, 8), (1000, 8, 256), (333, 3, 1000), (32768, 8, 256)]:
+        check_route(torch.randint(0, E, (T, k), generator=g, dtype=torch.int32), E)
+    # heavy skew: everything on one expert, and experts that receive nothing
+    check_route(torch.full((5000, 2), 3, dtype=torch.int32), 8)
+    _, ids = C.routing(4096, 8, 2, 1002)
+    check_route(ids, 8)
+
+
+def test_route_rejects_bad_ids():
+    ids = torch.tensor([[0, 9]], dtype=torch.int32, device=DEV)
+    with pytest.raises(ValueError):
+        B.route(ids, 4)
+    check_route(torch.tensor([[0, 3]], dtype=torch.int32), 4)
+
+
+def test_gather_rows():
+    g = torch.Generator().manual_seed(2)
+    for (T, H, k, dtype) in [(64, 4096, 2, torch.bfloat16), (33, 7168, 8, torch.bfloat16), (50, 56, 2, torch.float32),
+                             (9, 7, 3, torch.uint8)]:
+        src = torch.randint(0, 255, (T, H), generator=g).to(dtype)
+        idx = torch.randperm(T * k, generator=g).to(torch.int32)
+        out = B.gather_rows(src.to(DEV), idx.to(DEV), div=k)
+        assert torch.equal(out.cpu(), src[(idx // k).long()])
+
+
+def test_silu_and_mul():
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(77, 2 * 264, generator=g) * 3).to(torch.bfloat16)
+    out = B.silu_and_mul(x.to(DEV)).cpu().float()
+    ref = O.silu_and_mul_ref(x.float())
+    torch.testing.assert_close(out, ref, rtol=1e-2, atol=1e-2)
+
+
+def test_combine_topk():
+    g = torch.Generator().manual_seed(4)
+    T, k, H = 100, 3, 264
+    y = torch.randn(T * k, H, generator=g).to(torch.bfloat16)
+    w = torch.rand(T, k, generator=g)
+    inv = torch.randperm(T * k, generator=g).to(torch.int32)
+    out = B.combine_topk(y.to(DEV), inv.to(DEV), w.to(DEV), T, k).cpu().float()
+    ref = (y.float()[inv.long()].view(T, k, H) * w.view(T, k, 1)).sum(1)
+    torch.testing.assert_close(out, ref, rtol=1e-2, atol=1e-2)
+
+
+def test_quant_1x128_bit_exact():
+    z = load_npz("quant_1x128.npz")
+    x = torch.from_numpy(z["x"])
+    for inp in (x, x.to(torch.bfloat16)):
+        q, s = B.float8_groupwise_quantize(inp.to(DEV))
+        rq, rs = O.quant_1x128_ref(inp)
+        assert torch.equal(s.cpu(), rs)
+        assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
+    np.testing.assert_array_equal(B.float8_groupwise_quantize(x.to(DEV))[1].cpu().numpy(), z["scales"])
+    g = torch.Generator().manual_seed(5)
+    big = torch.randn(3, 500, 1024, generator=g).to(torch.bfloat16)
+    q, s = B.float8_groupwise_quantize(big.to(DEV))
+    rq, rs = O.quant_1x128_ref(big)
+    assert s.shape == (3, 500, 8) and torch.equal(s.cpu(), rs)
+    assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
+
+
+@pytest.mark.parametrize("cta", [1, 2])
+def test_fused_moe_golden(cta):
+    """Inputs and outputs of the reference's `torch_moe` (test_moe_gemm.py:16-30)."""
+    z = load_npz("torch_moe.npz")
+    for i in range(int(z["n_cases"])):
+        a, w1, w2 = (bf16_from_bits(z[f"{n}{i}"]).to(DEV) for n in ("a", "w1", "w2"))
+        tw = torch.from_numpy(z[f"topk_weight{i}"]).to(DEV)
+        ids = torch.from_numpy(z[f"topk_ids{i}"]).to(DEV)
+        ref = torch.from_numpy(z[f"out{i}"])
+        out = B.fused_moe(a, w1, w2, tw, ids, cta_group=cta).cpu().float()
+        assert O.rel_err(out, ref) <= BF16_REL_TOL
+        # the reference's own acceptance bound (test_moe_gemm.py:78)
+        assert torch.allclose(out, ref, atol=1e-2, rtol=0)
+
+
+def test_fused_moe_layer_and_inplace():
+    hidden, w1, w2, tw, ids = C.c3_mixtral_layer(T=256, H=512, I=768, E=8, k=2)
+    ref = O.torch_moe_ref(hidden, w1, w2, tw, ids)
+    h = hidden.to(DEV)
+    out = B.fused_moe(h, w1.to(DEV), w2.to(DEV), tw.to(DEV), ids.to(DEV))
+    assert O.rel_err(out.cpu().float(), ref) <= BF16_REL_TOL
+    ret = B.fused_moe(h, w1.to(DEV), w2.to(DEV), tw.to(DEV), ids.to(DEV), inplace=True)
+    assert ret.data_ptr() == h.data_ptr() and torch.equal(h, out)
