@@ -316,11 +316,12 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                 if constexpr (EPI == 1) {
                     uint32_t u[32];
                     tmem_ld_32x32(t_acc + static_cast<uint32_t>(128 + c * 32), u);
-                    tmem_ld_wait();
+                    tmem_ld_wait(v);
+                    tmem_ld_wait(u);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j]));
                 } else {
-                    tmem_ld_wait();
+                    tmem_ld_wait(v);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                 }
@@ -524,7 +525,9 @@ int grouped_gemm_launch(const GGLaunch& a) {
     p.n_out = a.epilogue == 1 ? a.N / 2 : a.N;
     p.n_tiles = a.epilogue == 1 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;
 
-    const int ctas = a.cta_group == 1 ? 1 : 2;
+    // A CTA pair computes 256 rows at a time; with few rows per group most of that tile
+    // would be padding, so small groups use the single-CTA 128-row tile.
+    const int ctas = a.cta_group == 1 ? 1 : a.cta_group == 2 ? 2 : (a.M / a.G >= 256 ? 2 : 1);
     const bool fp8 = a.elem_bytes == 1;
 #define B200MOE_LAUNCH(EB, SC, EP)                                                          \
     (ctas == 1 ? launch_variant<EB, 1, SC, EP>(tm_x, tm_w, p, di.sms, a.stream)              \
