@@ -5,7 +5,8 @@
 
 namespace b200moe {
 
-constexpr int kRouteMaxExperts = 4096;
+// Per-warp histograms of E counters must fit the default 48 KiB of dynamic shared memory.
+constexpr int kRouteMaxExperts = 2048;
 constexpr int kRouteMaxChunks = 1024;
 
 // Splits R ids into chunks for the routing kernels; scratch needed = num_chunks * E int32.

@@ -75,8 +75,8 @@ int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float
  * inv_perm[R] (flat index -> sorted position, -1 for an id outside [0,E)).
  * Takes the place of vLLM's moe_align_block_size as called at
  * kernels/triton/inference/col_major_moe_gemm/v0_moe_fused.py:138-180, without the
- * padding (the GEMM handles ragged groups).  `workspace` is scratch of at least
- * b200moe_route_workspace_bytes(R, E) bytes. */
+ * padding (the GEMM handles ragged groups).  E <= 2048.  `workspace` is scratch of at
+ * least b200moe_route_workspace_bytes(R, E) bytes. */
 int b200moe_route_workspace_bytes(int R, int E, size_t* bytes);
 int b200moe_route(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
                   int32_t* inv_perm, void* workspace, size_t workspace_bytes, int32_t* status,

@@ -43,6 +43,8 @@ def test_argument_errors_need_no_device():
     assert lib.b200moe_route_workspace_bytes(1000, 8, ctypes.byref(n)) == 0 and n.value == 4 * 8 * 4
     assert lib.b200moe_route_workspace_bytes(262144, 256, ctypes.byref(n)) == 0 and n.value == 1024 * 256 * 4
     assert lib.b200moe_route_workspace_bytes(10, 0, ctypes.byref(n)) == -1
+    assert lib.b200moe_route_workspace_bytes(10, 2048, ctypes.byref(n)) == 0
+    assert lib.b200moe_route_workspace_bytes(10, 2049, ctypes.byref(n)) == -1
     # null pointers / bad sizes are rejected before any CUDA call
     assert lib.b200moe_grouped_gemm_bf16(None, None, None, None, 8, 8, 8, 1, 8, 0, 0, 0, None, None) == -1
     assert lib.b200moe_swiglu(None, None, 4, 8, None) == -1

@@ -25,7 +25,7 @@ def check_route(ids, E):
 def test_route_bit_exact():
     g = torch.Generator().manual_seed(1)
     check_route(torch.tensor([[2, 3, 4], [1, 2, 4], [1, 3, 4], [1, 2, 3]], dtype=torch.int32), 5)  # docstring example
-    for (T, k, E) in [(1, 1, 1), (7, 2, 8), (4096, 2, 8), (1000, 8, 256), (333, 3, 1000), (32768, 8, 256)]:
+    for (T, k, E) in [(1, 1, 1), (7, 2, 8), (4096, 2, 8), (1000, 8, 256), (333, 3, 1000), (50, 2, 2048), (32768, 8, 256)]:
         check_route(torch.randint(0, E, (T, k), generator=g, dtype=torch.int32), E)
     # heavy skew: everything on one expert, and experts that receive nothing
     check_route(torch.full((5000, 2), 3, dtype=torch.int32), 8)
@@ -38,6 +38,8 @@ def test_route_rejects_bad_ids():
     with pytest.raises(ValueError):
         B.route(ids, 4)
     check_route(torch.tensor([[0, 3]], dtype=torch.int32), 4)
+    with pytest.raises(RuntimeError):  # more experts than the routing kernels support
+        B.route(torch.zeros(4, 2, dtype=torch.int32, device=DEV), 4096)
 
 
 def test_gather_rows():
