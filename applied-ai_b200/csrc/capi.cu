@@ -95,6 +95,14 @@ int b200moe_route(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* o
                         static_cast<cudaStream_t>(stream));
 }
 
+int b200moe_route_noalloc(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
+                          int32_t* inv_perm, int32_t* status, b200moe_stream_t stream) {
+    if (m_sizes == nullptr || offsets == nullptr) return kErrBadArgument;
+    if (R > 0 && (ids == nullptr || perm == nullptr || inv_perm == nullptr)) return kErrBadArgument;
+    return route_static_launch(ids, R, E, m_sizes, offsets, perm, inv_perm, status,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int b200moe_gather_rows(const void* src, const int32_t* idx, int div, void* dst, int rows, int64_t row_bytes,
                         int src_rows, b200moe_stream_t stream) {
     if (rows > 0 && (src == nullptr || idx == nullptr || dst == nullptr)) return kErrBadArgument;

@@ -11,6 +11,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "b200moe_internal.h"
 #include "moe_kernels.h"
 
@@ -170,6 +172,47 @@ int route_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* of
     route_scatter_kernel<<<blocks, kRouteWarps * 32, sizeof(int32_t) * (kRouteWarps + 1) * E, stream>>>(
         ids, R, E, chunk_len, num_chunks, counts, m_sizes, offsets, perm, inv_perm);
     return static_cast<int>(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------ routing, scratch held by the library
+//
+// Same three launches as route_launch, with the chunk counts kept in an array that is
+// part of the library image instead of a buffer from the caller.  Each GPU that loads
+// the library carries the array (1 MiB) until the process exits.
+constexpr int kRouteStaticInts = 1024 * 256;
+constexpr int kRouteStaticMaxDevices = 64;
+static __device__ __align__(256) int32_t g_route_static_counts[kRouteStaticInts];
+
+int route_static_capacity_ints() { return kRouteStaticInts; }
+
+int route_static_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
+                        int32_t* inv_perm, int32_t* status, cudaStream_t stream) {
+    int chunk_len = 0, num_chunks = 0;
+    if (int e = route_plan(R, E, &chunk_len, &num_chunks)) return e;
+    if (static_cast<long long>(num_chunks) * E > kRouteStaticInts) return kErrTooLarge;
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+    if (dev < 0 || dev >= kRouteStaticMaxDevices) return kErrBadArgument;
+    // In host code the array's name is only a handle for the runtime; the address the
+    // kernels need is a per-device value that has to be asked for, once, while that
+    // device is current.
+    static std::mutex mu;
+    static int32_t* dev_ptr[kRouteStaticMaxDevices] = {};
+    int32_t* counts = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            ce = cudaGetSymbolAddress(&p, g_route_static_counts);
+            if (ce != cudaSuccess) return static_cast<int>(ce);
+            dev_ptr[dev] = static_cast<int32_t*>(p);
+        }
+        counts = dev_ptr[dev];
+    }
+    // Every counts[c][e] with c < num_chunks is overwritten by the count kernel before it
+    // is read, so what an earlier call left in the array does not matter.
+    return route_launch(ids, R, E, m_sizes, offsets, perm, inv_perm, counts, status, stream);
 }
 
 // ------------------------------------------------------------------ gather

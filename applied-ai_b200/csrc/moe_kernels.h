@@ -13,6 +13,10 @@ constexpr int kRouteMaxChunks = 1024;
 int route_plan(int R, int E, int* chunk_len, int* num_chunks);
 int route_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
                  int32_t* inv_perm, int32_t* counts, int32_t* status, cudaStream_t stream);
+// Routing with the scratch in a fixed array inside the library (num_chunks * E <= capacity).
+int route_static_capacity_ints();
+int route_static_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
+                        int32_t* inv_perm, int32_t* status, cudaStream_t stream);
 int gather_rows_launch(const void* src, const int32_t* idx, int div, void* dst, int rows, long long row_bytes,
                        int src_rows, cudaStream_t stream);
 int swiglu_launch(const void* in, void* out, long long rows, int d, cudaStream_t stream);

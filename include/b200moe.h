@@ -82,6 +82,25 @@ int b200moe_route(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* o
                   int32_t* inv_perm, void* workspace, size_t workspace_bytes, int32_t* status,
                   b200moe_stream_t stream);
 
+/* b200moe_route for callers that have no device buffer to lend and no way to get one.
+ * (No counterpart in the reference: it exists for hosts such as an inference server
+ * that has handed every free byte of HBM to its own cache pool, or a plugin that runs
+ * under an allocator it does not own.  There cudaMalloc can fail outright, and even
+ * when it succeeds it stalls the whole device.)  Same inputs, outputs and ordering
+ * as b200moe_route; the chunk counts live in a 1 MiB array that is part of the library
+ * image, so every GPU that loads the library holds that 1 MiB until the process exits.
+ * Limit: chunks * E <= 262144, where chunks = ceil(R / max(256, 32*ceil(R/32768)));
+ * in practice any R with E <= 256, or E <= 2048 with R <= 32768.  Beyond that the call
+ * returns B200MOE_ETOOLARGE and enqueues nothing.  It never calls cudaMalloc, cudaFree
+ * or any allocating library routine.
+ * The first call on each device looks up the array's device address (the device must
+ * be current); make that first call before starting any stream capture.  All calls on a
+ * device share the one array: two calls whose kernels can overlap on the GPU (different
+ * streams, no ordering between them) race on it.  Nothing in it has to start at zero:
+ * each call overwrites every entry it later reads. */
+int b200moe_route_noalloc(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
+                          int32_t* inv_perm, int32_t* status, b200moe_stream_t stream);
+
 /* dst[p, :] = src[idx[p] / div, :] for p < rows; row_bytes bytes per row.  The
  * indexed load the reference's GEMM does per tile (v0_moe_fused.py:95, offs_token //
  * top_k), as one pass.  Entries with idx < 0 or a source row >= src_rows are skipped. */
