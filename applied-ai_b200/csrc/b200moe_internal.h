@@ -58,5 +58,7 @@ struct GGLaunch {
 };
 
 int grouped_gemm_launch(const GGLaunch& a);
+// FP8 with 1x128 activation scales [M, K/128] and 128x128 weight scales [G, ceil(N/128), K/128].
+int grouped_gemm_fp8_block_launch(const GGLaunch& a);
 
 }  // namespace b200moe

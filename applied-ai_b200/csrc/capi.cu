@@ -74,6 +74,33 @@ int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float
     return grouped_gemm_launch(a);
 }
 
+int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                       const int32_t* m_sizes, void* y, int M, int N, int K, int G, int64_t ldy,
+                                       int64_t y_col_group_stride, int epilogue, int cta_group, int32_t* status,
+                                       b200moe_stream_t stream) {
+    GGLaunch a{};
+    a.x = xq;
+    a.w = wq;
+    a.m_sizes = m_sizes;
+    a.y = y;
+    a.x_scale = x_scale;
+    a.w_scale = w_scale;
+    a.status = status;
+    a.ldy = ldy;
+    a.y_col_group_stride = y_col_group_stride;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.G = G;
+    a.elem_bytes = 1;
+    a.scale_mode = 2;
+    a.epilogue = epilogue;
+    a.cta_group = cta_group;
+    a.stream = static_cast<cudaStream_t>(stream);
+    if (ldy <= 0 || y_col_group_stride < 0) return kErrBadArgument;
+    return grouped_gemm_fp8_block_launch(a);
+}
+
 int b200moe_route_workspace_bytes(int R, int E, size_t* bytes) {
     if (bytes == nullptr) return kErrBadArgument;
     int chunk_len = 0, num_chunks = 0;

@@ -1,0 +1,293 @@
+// Pieces shared by the grouped-GEMM kernels: tile geometry, the shared-memory tail
+// (barriers + group tables), the ragged tile walk, the TMA producer loop and the
+// host-side tensor-map encoders.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b200moe_internal.h"
+#include "ptx.cuh"
+
+namespace b200moe {
+
+constexpr int kMaxGroups = 1024;
+constexpr int kRowsPerCta = 128;                    // accumulator rows (TMEM lanes) per CTA
+constexpr int kTileN = 256;                         // accumulator columns per tile
+constexpr int kRowBytes = 128;                      // one swizzle row: 64 bf16 or 128 e4m3 along K
+constexpr int kABytes = kRowsPerCta * kRowBytes;    // 16 KiB
+constexpr int kSubBoxBytes = 128 * kRowBytes;       // a 128-row box of w: 16 KiB
+constexpr int kTmemCols = 2 * kTileN;               // two accumulators
+
+template <int CTAS>
+struct StageCfg {
+    static constexpr int kBBytes = (2 / CTAS) * kSubBoxBytes;  // this CTA's share of the w box
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = CTAS == 1 ? 4 : 6;
+    static constexpr int kRingBytes = kStages * kStageBytes;   // 192 KiB either way
+};
+
+struct SmemTail {
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    int invalid;
+    int total_tiles;
+    int row_off[kMaxGroups + 1];
+    int tile_off[kMaxGroups + 1];
+};
+
+template <int CTAS>
+constexpr size_t gg_smem_bytes() {
+    return 1024 + StageCfg<CTAS>::kRingBytes + sizeof(SmemTail);
+}
+
+// Carves the dynamic shared memory: a 1024-byte aligned stage ring followed by the tail.
+struct SmemView {
+    uint32_t ring_addr;
+    SmemTail* tail;
+};
+template <int CTAS>
+__device__ __forceinline__ SmemView carve_smem(uint8_t* smem_raw) {
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    SmemView v;
+    v.ring_addr = (raw_addr + 1023u) & ~1023u;
+    v.tail = reinterpret_cast<SmemTail*>(smem_raw + (v.ring_addr - raw_addr) + StageCfg<CTAS>::kRingBytes);
+    return v;
+}
+
+__device__ __forceinline__ void report(int32_t* status, int code) {
+    if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+struct TileCoord {
+    int g, row0, row_end, n_idx;
+};
+
+// Maps a global tile number to its group and position.  `g` only moves forward.
+__device__ __forceinline__ TileCoord locate_tile(int t, int& g, const int* tile_off, const int* row_off,
+                                                 int tile_rows) {
+    while (tile_off[g + 1] <= t) ++g;
+    const int local = t - tile_off[g];
+    const int m_g = row_off[g + 1] - row_off[g];
+    const int tiles_m = (m_g + tile_rows - 1) / tile_rows;
+    TileCoord c;
+    c.g = g;
+    c.row0 = row_off[g] + (local % tiles_m) * tile_rows;
+    c.row_end = row_off[g + 1];
+    c.n_idx = local / tiles_m;
+    return c;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
+
+// Stores 32 consecutive fp32 values of one output row as bf16 at columns [col, col+32),
+// clipped to n_out columns; 16-byte stores when the run is whole and aligned.
+__device__ __forceinline__ void store_row_chunk(__nv_bfloat16* y_row, int col, int n_out, const float* f) {
+    if (col >= n_out) return;
+    __nv_bfloat16* dst = y_row + col;
+    if ((col + 32 <= n_out) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16x2(f[q * 8 + 0], f[q * 8 + 1]);
+            o.y = pack_bf16x2(f[q * 8 + 2], f[q * 8 + 3]);
+            o.z = pack_bf16x2(f[q * 8 + 4], f[q * 8 + 5]);
+            o.w = pack_bf16x2(f[q * 8 + 6], f[q * 8 + 7]);
+            d4[q] = o;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col + j < n_out) dst[j] = __float2bfloat16_rn(f[j]);
+    }
+}
+
+// Run by ONE warp: exclusive prefix sums of rows and tiles over the groups (32 groups per
+// step), validation of m_sizes, and initialisation of the barriers.  `acc_empty_count` is
+// the number of arrivals that hand an accumulator back to the MMA issuer.
+template <int CTAS>
+__device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GGParams& p, int lane, int tile_rows,
+                                                          int acc_empty_count) {
+    int row_carry = 0, tile_carry = 0, bad = 0;
+    for (int base = 0; base < p.G; base += 32) {
+        const int g = base + lane;
+        int m = g < p.G ? p.m_sizes[g] : 0;
+        if (m < 0) {
+            bad = 1;
+            m = 0;
+        }
+        int tiles = ((m + tile_rows - 1) / tile_rows) * p.n_tiles;
+        int rs = m, ts = tiles;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int r2 = __shfl_up_sync(0xffffffffu, rs, d);
+            const int t2 = __shfl_up_sync(0xffffffffu, ts, d);
+            if (lane >= d) {
+                rs += r2;
+                ts += t2;
+            }
+        }
+        if (g < p.G) {
+            st->row_off[g] = row_carry + rs - m;
+            st->tile_off[g] = tile_carry + ts - tiles;
+        }
+        row_carry += __shfl_sync(0xffffffffu, rs, 31);
+        tile_carry += __shfl_sync(0xffffffffu, ts, 31);
+        if (row_carry > p.M) bad = 1;  // also stops int overflow of the running sum
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) {
+        st->row_off[p.G] = row_carry;
+        st->tile_off[p.G] = tile_carry;
+        st->total_tiles = bad ? 0 : tile_carry;
+        st->invalid = bad;
+        if (bad) report(p.status, kStatusBadGroupSizes);
+        for (int s = 0; s < StageCfg<CTAS>::kStages; ++s) {
+            mbar_init(&st->full[s], 1);
+            mbar_init(&st->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&st->acc_full[b], 1);
+            mbar_init(&st->acc_empty[b], acc_empty_count);
+        }
+        mbar_init_fence();
+    }
+}
+
+// TMA producer, run by ONE thread per CTA: for every tile of this cluster and every
+// 128-byte slice of K, wait for a free stage and fetch this CTA's 128 rows of x and its
+// share of the tile's two 128-row boxes of w[g] (rows nb0.. and nb1..).
+template <int CTAS, bool SWIGLU>
+__device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUtensorMap* tm_w, SmemTail* st,
+                                              uint32_t ring_addr, const GGParams& p, uint32_t cta_rank,
+                                              int cluster_id, int num_clusters, int elems_per_stage, int num_kb) {
+    using Cfg = StageCfg<CTAS>;
+    constexpr int kTileRows = kRowsPerCta * CTAS;
+    constexpr uint32_t kTxBytes = static_cast<uint32_t>(Cfg::kStageBytes) * CTAS;
+    volatile int* abort_flag = &st->abort_flag;
+    const int total_tiles = st->total_tiles;
+    int g = 0, stage = 0;
+    uint32_t phase = 0;
+    for (int t = cluster_id; t < total_tiles; t += num_clusters) {
+        const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
+        const int row0 = tc.row0 + static_cast<int>(cta_rank) * kRowsPerCta;
+        const int nb0 = SWIGLU ? tc.n_idx * 128 : tc.n_idx * kTileN;
+        const int nb1 = SWIGLU ? p.n_out + tc.n_idx * 128 : tc.n_idx * kTileN + 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag)) {
+                report(p.status, kStatusTimeoutProducer);
+                return;
+            }
+            const uint32_t a_dst = ring_addr + stage * Cfg::kStageBytes;
+            const uint32_t b_dst = a_dst + kABytes;
+            const int k0 = kb * elems_per_stage;
+            if constexpr (CTAS == 1) {
+                const uint32_t bar = smem_u32(&st->full[stage]);
+                mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                tma_load_2d(tm_x, bar, a_dst, k0, row0);
+                tma_load_3d(tm_w, bar, b_dst, k0, nb0, tc.g);
+                tma_load_3d(tm_w, bar, b_dst + kSubBoxBytes, k0, nb1, tc.g);
+            } else {
+                // Bytes of both CTAs are counted on the leader's barrier.
+                const uint32_t bar = mapa_shared(smem_u32(&st->full[stage]), 0);
+                if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                tma_load_2d_pair(tm_x, bar, a_dst, k0, row0);
+                tma_load_3d_pair(tm_w, bar, b_dst, k0, cta_rank == 0 ? nb0 : nb1, tc.g);
+            }
+            if (++stage == Cfg::kStages) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so the library links against the
+// CUDA runtime only.
+inline EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+// x viewed as [rows, K]; box = 128 rows x 128 bytes, 128-byte swizzle.
+inline int encode_x_map(CUtensorMap* m, const void* x, int rows, int K, int elem_bytes) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return kErrNoDriverEntry;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * elem_bytes};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                     const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
+}
+
+// w viewed as [G, rows_per_group, K]; box = 1 group x 128 rows x 128 bytes.  The group
+// is its own dimension so a box that runs past a group's last row is zero-filled
+// instead of reading the next expert's weights.
+inline int encode_w_map(CUtensorMap* m, const void* w, int G, int rows_per_group, int K, int elem_bytes) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return kErrNoDriverEntry;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows_per_group),
+                          static_cast<cuuint64_t>(G)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(K) * elem_bytes,
+                             static_cast<cuuint64_t>(K) * elem_bytes * rows_per_group};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                     const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    int cc_major = 0, cc_minor = 0;
+};
+inline int get_device_info(DeviceInfo* out) {
+    static thread_local int cached_dev = -1;
+    static thread_local DeviceInfo cached;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev != cached_dev) {
+        cudaDeviceProp prop;
+        e = cudaGetDeviceProperties(&prop, dev);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        cached.sms = prop.multiProcessorCount;
+        cached.cc_major = prop.major;
+        cached.cc_minor = prop.minor;
+        cached_dev = dev;
+    }
+    *out = cached;
+    return 0;
+}
+
+}  // namespace b200moe

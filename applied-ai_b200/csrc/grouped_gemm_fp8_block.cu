@@ -1,0 +1,304 @@
+// FP8 grouped GEMM with block-wise scales (the DeepSeek-V3 recipe):
+//     y[m, n] = sum over K blocks kb of
+//               (xq[m, kb] . wq[g][n, kb]) * x_scale[m, kb] * w_scale[g][n / 128][kb]
+// xq [M, K] e4m3 with one fp32 scale per row and 128 columns (1x128), wq [G, N, K] e4m3
+// with one fp32 scale per 128x128 block, y bf16.  The reference has no such kernel (its
+// block-wise path lives in FBGEMM, kernels/needs_perf_help/fp8_gemm_bench.py:16-21); the
+// 1x128 scale convention is that of kernels/triton/inference/fp8/float8_groupwise_quant.py.
+//
+// The scales change along K, so they cannot wait for the end of the tile.  One
+// shared-memory stage holds exactly one 128-deep K block.  The MMA issuer accumulates
+// each block on its own (4 MMAs, the first one overwriting) into one of two 256-column
+// TMEM buffers and publishes it; the epilogue warps pull it out with tcgen05.ld and fold
+// it into fp32 REGISTER accumulators with the block's combined scale while the tensor
+// core already works on the next block in the other buffer.
+//
+// 384 threads in three warpgroups: warp 0 TMA producer, warp 1 MMA issuer (warps 2, 3
+// only help set up), warps 4..11 epilogue.  Epilogue warp w owns TMEM lanes 32*(w%4)..
+// (a hardware rule) and half of the tile's columns, i.e. 128 accumulators per thread;
+// setmaxnreg moves registers from the first warpgroup to the two epilogue warpgroups so
+// those accumulators stay in registers.  Tile shapes, scheduler and the CTA-pair mode are
+// those of the bf16 kernel (grouped_gemm.cu).
+#include "gg_common.cuh"
+
+namespace b200moe {
+
+constexpr int kBlkThreads = 384;
+constexpr int kBlkEpiWarps = 8;
+
+template <int CTAS, int EPI>
+__global__ void __launch_bounds__(kBlkThreads, 1)
+gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                    const GGParams p) {
+#if defined(__CUDA_ARCH_FEAT_SM100_ALL)
+    using Cfg = StageCfg<CTAS>;
+    constexpr int kTileRows = kRowsPerCta * CTAS;
+    constexpr uint32_t kIdesc = make_idesc(true, kTileRows, kTileN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const SmemView sv = carve_smem<CTAS>(smem_raw);
+    const uint32_t ring_addr = sv.ring_addr;
+    SmemTail* st = sv.tail;
+    volatile int* abort_flag = &st->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = CTAS == 1 ? 0u : cluster_ctarank();
+    const int cluster_id = blockIdx.x / CTAS;
+    const int num_clusters = gridDim.x / CTAS;
+
+    if (threadIdx.x == 0) {
+        st->abort_flag = 0;
+        st->invalid = 0;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        build_tables_and_barriers<CTAS>(st, p, lane, kTileRows, kBlkEpiWarps * CTAS);
+        if (lane == 0) {
+            prefetch_tensormap(&tm_x);
+            prefetch_tensormap(&tm_w);
+        }
+    } else if (warp == 1) {
+        tmem_alloc<CTAS>(&st->tmem_base, kTmemCols);
+        tmem_relinquish<CTAS>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();
+    tc_fence_after();
+
+    const uint32_t tmem_base = st->tmem_base;
+    const int total_tiles = st->total_tiles;
+    const int num_kb = p.K / 128;  // the launcher guarantees K % 128 == 0
+
+    // Register budget per scheduler partition (16384): one light warp + two epilogue warps.
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      if (warp == 0) {
+        if (lane == 0)
+            producer_loop<CTAS, EPI == 1>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters, 128,
+                                          num_kb);
+      } else if (warp == 1) {
+        // ================= MMA issuer: one K block per stage, one TMEM buffer per K block
+        if (lane == 0 && cta_rank == 0) {
+            int stage = 0, buf = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
+                        report(p.status, kStatusTimeoutMmaAcc);
+                        ok = false;
+                        break;
+                    }
+                    if (!mbar_wait(&st->full[stage], phase, abort_flag)) {
+                        report(p.status, kStatusTimeoutMmaFull);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kTileN);
+                    const uint32_t a_addr = ring_addr + stage * Cfg::kStageBytes;
+                    const uint64_t a_desc = make_sw128_kmajor_desc(a_addr);
+                    const uint64_t b_desc = make_sw128_kmajor_desc(a_addr + kABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma<CTAS, true>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, k > 0 ? 1u : 0u);
+                    umma_commit<CTAS>(&st->empty[stage]);
+                    umma_commit<CTAS>(&st->acc_full[buf]);
+                    if (++stage == Cfg::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                    buf ^= 1;
+                    if (buf == 0) acc_phase ^= 1u;
+                }
+            }
+        }
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        // ================= epilogue / promotion (8 warps)
+        const int ew = warp - 4;          // 0..7
+        const int quarter = warp & 3;     // TMEM lane quarter this warp may read
+        const int half = ew >> 2;         // which half of the tile's columns
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t acc_empty_leader =
+            CTAS == 1 ? smem_u32(&st->acc_empty[0]) : mapa_shared(smem_u32(&st->acc_empty[0]), 0);
+        __nv_bfloat16* const y = static_cast<__nv_bfloat16*>(p.y);
+        const int kblocks = num_kb;                    // scales per row of x
+        const int nblocks = (p.N + 127) / 128;         // scale blocks per expert along N
+        int g = 0, buf = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
+            const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
+            const int row = tc.row0 + static_cast<int>(cta_rank) * kRowsPerCta + quarter * 32 + lane;
+            const bool row_ok = row < tc.row_end;
+            const float* xs_row = p.x_scale + static_cast<size_t>(row_ok ? row : 0) * kblocks;
+            // The thread's 128 columns are four runs of 32: two scale blocks at most.
+            //   plain : columns half*128 + [0,128)            -> scale block 2*n_idx + half
+            //   SwiGLU: gate columns half*64 + [0,64) (block n_idx) and the matching up
+            //           columns 128 + half*64 + [0,64) (block I/128 + n_idx)
+            const int col_a = EPI == 1 ? half * 64 : half * 128;
+            const int col_b = EPI == 1 ? 128 + half * 64 : half * 128 + 64;
+            const int blk_a = EPI == 1 ? tc.n_idx : 2 * tc.n_idx + half;
+            const int blk_b = EPI == 1 ? p.n_out / 128 + tc.n_idx : blk_a;
+            const float* ws_a = p.w_scale + (static_cast<size_t>(tc.g) * nblocks + min(blk_a, nblocks - 1)) * kblocks;
+            const float* ws_b = p.w_scale + (static_cast<size_t>(tc.g) * nblocks + min(blk_b, nblocks - 1)) * kblocks;
+
+            float acc[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+
+            float xs_next = row_ok ? __ldg(xs_row) : 0.0f;
+            float wa_next = __ldg(ws_a), wb_next = __ldg(ws_b);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const float sa = xs_next * wa_next;
+                const float sb = xs_next * wb_next;
+                if (kb + 1 < num_kb) {  // fetch the next block's scales while waiting
+                    xs_next = row_ok ? __ldg(xs_row + kb + 1) : 0.0f;
+                    wa_next = __ldg(ws_a + kb + 1);
+                    wb_next = __ldg(ws_b + kb + 1);
+                }
+                int got = 1;
+                if (lane == 0) got = mbar_wait(&st->acc_full[buf], acc_phase, abort_flag) ? 1 : 0;
+                got = __shfl_sync(0xffffffffu, got, 0);
+                if (!got) {
+                    if (lane == 0) report(p.status, kStatusTimeoutEpilogue);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t t_acc = tmem_base + lane_base + static_cast<uint32_t>(buf * kTileN);
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    uint32_t v0[32], v1[32];
+                    const uint32_t c = static_cast<uint32_t>(h2 == 0 ? col_a : col_b);
+                    tmem_ld_32x32(t_acc + c, v0);
+                    tmem_ld_32x32(t_acc + c + 32, v1);
+                    tmem_ld_wait(v0);
+                    tmem_ld_wait(v1);
+                    const float s = h2 == 0 ? sa : sb;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        acc[h2 * 64 + j] = fmaf(__uint_as_float(v0[j]), s, acc[h2 * 64 + j]);
+                        acc[h2 * 64 + 32 + j] = fmaf(__uint_as_float(v1[j]), s, acc[h2 * 64 + 32 + j]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
+                buf ^= 1;
+                if (buf == 0) acc_phase ^= 1u;
+            }
+            if (!ok) break;
+
+            // ---- store: the thread's row, its (up to) 128 output columns
+            if (row_ok) {
+                __nv_bfloat16* const y_row =
+                    y + static_cast<size_t>(row) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
+                if constexpr (EPI == 1) {
+                    const int col = tc.n_idx * 128 + half * 64;  // 64 output columns: silu(gate) * up
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        float f[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = silu_mul(acc[c * 32 + j], acc[64 + c * 32 + j]);
+                        store_row_chunk(y_row, col + c * 32, p.n_out, f);
+                    }
+                } else {
+                    const int col = tc.n_idx * kTileN + half * 128;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) store_row_chunk(y_row, col + c * 32, p.n_out, &acc[c * 32]);
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<CTAS>(tmem_base, kTmemCols);
+    }
+#else
+    if (threadIdx.x == 0 && blockIdx.x == 0) report(p.status, kStatusWrongArch);
+#endif
+}
+
+template <int CTAS, int EPI>
+static int launch_block_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const GGParams& p, int sms,
+                                cudaStream_t stream) {
+    auto kernel = gg_fp8_block_kernel<CTAS, EPI>;
+    constexpr size_t smem = gg_smem_bytes<CTAS>();
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured_dev = dev;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>((sms / CTAS) * CTAS), 1, 1);
+    cfg.blockDim = dim3(kBlkThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, p));
+}
+
+int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
+    if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0 || a.x == nullptr || a.w == nullptr || a.y == nullptr ||
+        a.m_sizes == nullptr || a.x_scale == nullptr || a.w_scale == nullptr)
+        return kErrBadArgument;
+    if (a.G > kMaxGroups) return kErrTooManyGroups;
+    if (a.K % 128 != 0) return kErrAlignment;  // whole scale blocks along K
+    if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.w) & 15u)) return kErrAlignment;
+    if (a.epilogue != 0 && a.epilogue != 1) return kErrBadArgument;
+    if (a.epilogue == 1 && (a.N % 256 != 0)) return kErrBadArgument;  // gate and up halves in whole scale blocks
+    if (a.M == 0) return 0;
+
+    DeviceInfo di;
+    if (int e = get_device_info(&di)) return e;
+    if (di.cc_major != 10) return kErrWrongDevice;
+    CUtensorMap tm_x, tm_w;
+    if (int e = encode_x_map(&tm_x, a.x, a.M, a.K, 1)) return e;
+    if (int e = encode_w_map(&tm_w, a.w, a.G, a.N, a.K, 1)) return e;
+
+    GGParams p;
+    p.m_sizes = a.m_sizes;
+    p.y = a.y;
+    p.x_scale = a.x_scale;
+    p.w_scale = a.w_scale;
+    p.status = a.status;
+    p.M = a.M;
+    p.N = a.N;
+    p.K = a.K;
+    p.G = a.G;
+    p.ldy = a.ldy;
+    p.y_col_group_stride = a.y_col_group_stride;
+    p.n_out = a.epilogue == 1 ? a.N / 2 : a.N;
+    p.n_tiles = a.epilogue == 1 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;
+
+    const int ctas = a.cta_group == 1 ? 1 : a.cta_group == 2 ? 2 : (a.M / a.G >= 256 ? 2 : 1);
+    if (a.epilogue == 0)
+        return ctas == 1 ? launch_block_variant<1, 0>(tm_x, tm_w, p, di.sms, a.stream)
+                         : launch_block_variant<2, 0>(tm_x, tm_w, p, di.sms, a.stream);
+    return ctas == 1 ? launch_block_variant<1, 1>(tm_x, tm_w, p, di.sms, a.stream)
+                     : launch_block_variant<2, 1>(tm_x, tm_w, p, di.sms, a.stream);
+}
+
+}  // namespace b200moe

@@ -145,3 +145,39 @@ def grouped_gemm_fp8_rowwise(x, w, m_sizes, x_scale, w_scale, *, cta_group=0, ch
     if _default_check if check is None else check:
         raise_on_status(word, "grouped_gemm_fp8_rowwise")
     return y
+
+
+def grouped_gemm_fp8_blockwise(x, w, m_sizes, x_scale, w_scale, *, epilogue="none", cta_group=0, check=None):
+    """FP8 grouped GEMM with 1x128 activation scales and 128x128 weight-block scales -> bf16.
+
+    x [M, K], w [G*N, K] or [G, N, K] float8_e4m3fn; x_scale [M, K/128] fp32 (as produced by
+    float8_groupwise_quantize); w_scale [G, ceil(N/128), K/128] fp32 (quantize_fp8_block).
+    epilogue="swiglu": w[g] = [gate; up], output has N/2 columns."""
+    m_sizes, G, M, N, K = _prepare(x, w, m_sizes, torch.float8_e4m3fn)
+    _require(K % 128 == 0, "K must be a multiple of 128 for block-wise scales")
+    epi = {"none": 0, "swiglu": 1}.get(epilogue)
+    _require(epi is not None, "epilogue must be 'none' or 'swiglu'")
+    if epi == 1:
+        _require(N % 256 == 0, "SwiGLU with block-wise scales needs N (gate+up rows) to be a multiple of 256")
+    nblk = (N + 127) // 128
+    _require(isinstance(x_scale, torch.Tensor) and isinstance(w_scale, torch.Tensor), "scales must be tensors")
+    _require(x_scale.device == x.device and w_scale.device == x.device, "scales must be on the same device as x")
+    _require(x_scale.dtype == torch.float32 and w_scale.dtype == torch.float32, "scales must be float32")
+    _require(x_scale.is_contiguous() and w_scale.is_contiguous(), "scales must be contiguous")
+    _require(tuple(x_scale.shape) == (M, K // 128), f"x_scale must be [M, K/128] = [{M}, {K // 128}]")
+    _require(w_scale.numel() == G * nblk * (K // 128), f"w_scale must be [G, ceil(N/128), K/128] = [{G}, {nblk}, {K // 128}]")
+    n_out = N // 2 if epi == 1 else N
+    y = torch.empty((M, n_out), device=x.device, dtype=torch.bfloat16)
+    if M == 0:
+        return y
+    lib = _lib.load()
+    word = _status_word(x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.b200moe_grouped_gemm_fp8_blockwise(x.data_ptr(), w.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
+                                                    m_sizes.data_ptr(), y.data_ptr(), M, N, K, G, n_out, 0, epi,
+                                                    cta_group, word.data_ptr(), stream)
+    _lib.check(rc, "grouped_gemm_fp8_blockwise")
+    if _default_check if check is None else check:
+        raise_on_status(word, "grouped_gemm_fp8_blockwise")
+    return y

@@ -44,13 +44,19 @@ def quantize_fp8_row(w):
 
 
 def quantize_fp8_block(w, block_n=128, block_k=128):
-    """128x128-block e4m3 quantisation of a weight [..., N, K] (N, K multiples of the
-    block): returns (q [..., N, K], scales [..., N/128, K/128] fp32) with the same scale
-    formula as the 1x128 quantiser.  Set-up code (run once per weight), plain torch."""
+    """128x128-block e4m3 quantisation of a weight [..., N, K] (K a multiple of the block; a
+    ragged last block along N is allowed): returns (q [..., N, K], scales
+    [..., ceil(N/128), K/128] fp32) with the same scale formula as the 1x128 quantiser.
+    Set-up code (run once per weight), plain torch."""
     *lead, N, K = w.shape
-    if N % block_n or K % block_k:
-        raise ValueError("N and K must be multiples of the block size")
-    f = w.float().reshape(*lead, N // block_n, block_n, K // block_k, block_k)
+    if K % block_k:
+        raise ValueError("K must be a multiple of the block size")
+    nb = (N + block_n - 1) // block_n
+    f = w.float()
+    if nb * block_n != N:
+        f = torch.nn.functional.pad(f, (0, 0, 0, nb * block_n - N))
+    f = f.reshape(*lead, nb, block_n, K // block_k, block_k)
     scale = f.abs().amax(dim=(-3, -1)).clamp_min(1e-12) / 448.0
     q = (f / scale[..., :, None, :, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
-    return q.reshape(*lead, N, K), scale
+    q = q.reshape(*lead, nb * block_n, K)[..., :N, :].contiguous()
+    return q, scale

@@ -70,6 +70,18 @@ int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float
                                      int64_t y_col_group_stride, int cta_group, int32_t* status,
                                      b200moe_stream_t stream);
 
+/* Block-wise scaled FP8 (1x128 activation scales, 128x128 weight scales):
+ *   y[m,n] = sum_kb (xq[m, kb*128:(kb+1)*128] . wq[g][n, same]) * x_scale[m, kb] * w_scale[g][n/128][kb]
+ * xq [M,K], wq [G,N,K] float8_e4m3fn; x_scale [M, K/128] fp32; w_scale [G, ceil(N/128), K/128]
+ * fp32; y bf16; K a multiple of 128.  epilogue = B200MOE_EPI_SWIGLU (N a multiple of 256)
+ * writes silu(gate)*up with N/2 columns.  Not present in the reference (its block-wise
+ * kernels are the absent FBGEMM ones named at kernels/needs_perf_help/fp8_gemm_bench.py:16-21);
+ * the activation-scale convention is float8_groupwise_quant.py:36-46. */
+int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                       const int32_t* m_sizes, void* y, int M, int N, int K, int G, int64_t ldy,
+                                       int64_t y_col_group_stride, int epilogue, int cta_group, int32_t* status,
+                                       b200moe_stream_t stream);
+
 /* Routing: stable counting sort of ids[R] (R = tokens*top_k, flat index t*top_k + j)
  * by expert.  m_sizes[E], offsets[E+1], perm[R] (sorted position -> flat index),
  * inv_perm[R] (flat index -> sorted position, -1 for an id outside [0,E)).
