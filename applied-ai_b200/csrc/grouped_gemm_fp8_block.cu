@@ -161,9 +161,8 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     wa_next = __ldg(ws_a + kb + 1);
                     wb_next = __ldg(ws_b + kb + 1);
                 }
-                int got = 1;
-                if (lane == 0) got = mbar_wait(&st->acc_full[buf], acc_phase, abort_flag) ? 1 : 0;
-                got = __shfl_sync(0xffffffffu, got, 0);
+                // every lane polls: the flip is seen without a shuffle hop
+                const int got = __all_sync(0xffffffffu, mbar_wait(&st->acc_full[buf], acc_phase, abort_flag) ? 1 : 0);
                 if (!got) {
                     if (lane == 0) report(p.status, kStatusTimeoutEpilogue);
                     ok = false;
@@ -171,24 +170,29 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 }
                 tc_fence_after();
                 const uint32_t t_acc = tmem_base + lane_base + static_cast<uint32_t>(buf * kTileN);
+                // Four runs of 32 columns through two staging buffers; the TMEM buffer goes back
+                // to the MMA issuer as soon as the last load has landed, before the last FMAs.
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32(t_acc + static_cast<uint32_t>(col_a), v0);
+                tmem_ld_32x32(t_acc + static_cast<uint32_t>(col_a + 32), v1);
+                tmem_ld_wait(v0);
+                tmem_ld_wait(v1);
 #pragma unroll
-                for (int h2 = 0; h2 < 2; ++h2) {
-                    uint32_t v0[32], v1[32];
-                    const uint32_t c = static_cast<uint32_t>(h2 == 0 ? col_a : col_b);
-                    tmem_ld_32x32(t_acc + c, v0);
-                    tmem_ld_32x32(t_acc + c + 32, v1);
-                    tmem_ld_wait(v0);
-                    tmem_ld_wait(v1);
-                    const float s = h2 == 0 ? sa : sb;
+                for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(v0[j]), sa, acc[j]);
+                tmem_ld_32x32(t_acc + static_cast<uint32_t>(col_b), v0);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        acc[h2 * 64 + j] = fmaf(__uint_as_float(v0[j]), s, acc[h2 * 64 + j]);
-                        acc[h2 * 64 + 32 + j] = fmaf(__uint_as_float(v1[j]), s, acc[h2 * 64 + 32 + j]);
-                    }
-                }
+                for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(v1[j]), sa, acc[32 + j]);
+                tmem_ld_32x32(t_acc + static_cast<uint32_t>(col_b + 32), v1);
+                tmem_ld_wait(v0);
+                tmem_ld_wait(v1);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    acc[64 + j] = fmaf(__uint_as_float(v0[j]), sb, acc[64 + j]);
+                    acc[96 + j] = fmaf(__uint_as_float(v1[j]), sb, acc[96 + j]);
+                }
                 buf ^= 1;
                 if (buf == 0) acc_phase ^= 1u;
             }

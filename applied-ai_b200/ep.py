@@ -1,0 +1,161 @@
+"""Expert-parallel MoE layer: experts sharded across ranks, tokens data-parallel.
+
+Rank r of P owns experts [r*E/P, (r+1)*E/P) and T/P tokens.  One exchange each way:
+
+    route by global expert  ->  counts all-to-all  ->  payload all-to-all (rows sorted by
+    destination rank, then expert)  ->  re-sort arrivals by local expert  ->  grouped GEMM
+    (gate+up, SwiGLU)  ->  grouped GEMM (down)  ->  back to arrival order  ->  return
+    all-to-all  ->  weighted top-k combine on the home rank
+
+The reference has no distributed code at all (`fused_moe` assumes every expert is local,
+kernels/triton/inference/col_major_moe_gemm/v0_moe_fused.py:249); this layer extends the
+same computation to the expert-parallel configuration of the benchmark.  The collectives
+are torch.distributed all_to_all_single (NCCL over NVLink on GPUs); received rows land
+in local memory before any kernel touches them.
+
+Every routed row is computed by the same kernel with the same reduction order whatever P
+is, and the combine sums in fixed top-k order on the home rank, so outputs do not depend
+on the number of ranks.
+
+The compute steps come from an `ops` object.  The default, `CudaOps`, calls
+libb200moe.so; there is no CPU implementation in this package (the CPU tests of the
+exchange logic inject their own checker ops).
+"""
+import torch
+import torch.distributed as dist
+
+
+class CudaOps:
+    """The layer's compute steps on the GPU.  mode: "bf16" or "fp8_blockwise"."""
+
+    def __init__(self, w1, w2, mode="bf16", cta_group=0):
+        from . import groupgemm, moe, quant
+        self._gg, self._moe, self._quant = groupgemm, moe, quant
+        self.mode = mode
+        self.cta_group = cta_group
+        if mode == "bf16":
+            self.w1, self.w2 = w1.contiguous(), w2.contiguous()
+        elif mode == "fp8_blockwise":
+            self.w1, self.w1_scale = self._quantize_weight(w1)
+            self.w2, self.w2_scale = self._quantize_weight(w2)
+        else:
+            raise ValueError("mode must be 'bf16' or 'fp8_blockwise'")
+
+    def _quantize_weight(self, w):
+        if w.dtype == torch.float8_e4m3fn:
+            raise ValueError("pass unquantised weights; block scales are computed here")
+        q = torch.empty(w.shape, dtype=torch.float8_e4m3fn, device=w.device)
+        s = torch.empty(w.shape[0], (w.shape[1] + 127) // 128, w.shape[2] // 128, dtype=torch.float32,
+                        device=w.device)
+        for e in range(w.shape[0]):  # one expert at a time bounds the fp32 temporaries
+            q[e], s[e] = self._quant.quantize_fp8_block(w[e])
+        return q, s
+
+    def route(self, ids, num_experts):
+        return self._moe.route(ids, num_experts, check=False)
+
+    def gather(self, src, idx, div=1):
+        return self._moe.gather_rows(src, idx, div=div)
+
+    def dispatch_payloads(self, hidden):
+        """What travels per token: the bf16 row, or its e4m3 bytes plus the 1x128 scales."""
+        if self.mode == "bf16":
+            return [hidden]
+        q, s = self._quant.float8_groupwise_quantize(hidden)
+        return [q.view(torch.uint8), s]
+
+    def expert_ffn(self, rows, m_sizes):
+        """rows: payload tensors sorted by local expert -> [R, H] bf16."""
+        gg = self._gg
+        if self.mode == "bf16":
+            h = gg.grouped_gemm(rows[0], self.w1, m_sizes, epilogue="swiglu", check=False, cta_group=self.cta_group)
+            return gg.grouped_gemm(h, self.w2, m_sizes, check=False, cta_group=self.cta_group)
+        xq, xs = rows[0].view(torch.float8_e4m3fn), rows[1]
+        h = gg.grouped_gemm_fp8_blockwise(xq, self.w1, m_sizes, xs, self.w1_scale, epilogue="swiglu", check=False,
+                                          cta_group=self.cta_group)
+        hq, hs = self._quant.float8_groupwise_quantize(h)
+        return gg.grouped_gemm_fp8_blockwise(hq, self.w2, m_sizes, hs, self.w2_scale, check=False,
+                                             cta_group=self.cta_group)
+
+    def combine(self, y, inv_perm, topk_weights, num_tokens, top_k):
+        return self._moe.combine_topk(y, inv_perm, topk_weights, num_tokens, top_k)
+
+
+def expert_ids_from_counts(recv_counts, total):
+    """Local expert id of every received row.  recv_counts [P, E_local]: rows arrive
+    grouped by source rank and, inside one source, by expert."""
+    P, e_local = recv_counts.shape
+    ids = torch.arange(e_local, device=recv_counts.device, dtype=torch.int32).repeat(P)
+    return torch.repeat_interleave(ids, recv_counts.reshape(-1).to(torch.int64), output_size=total)
+
+
+class ExpertParallelMoE:
+    """One MoE FFN layer under expert parallelism.
+
+    ops          compute steps holding this rank's expert weights (CudaOps)
+    num_experts  global expert count E (divisible by the group size)
+    group        torch.distributed process group (None: default group, or no exchange at
+                 all when torch.distributed is not initialised — the single-GPU case)
+    """
+
+    def __init__(self, ops, num_experts, group=None):
+        self.ops = ops
+        self.group = group
+        self.E = int(num_experts)
+        self.P = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        if self.E % self.P:
+            raise ValueError(f"{self.E} experts cannot be split evenly over {self.P} ranks")
+        self.e_local = self.E // self.P
+        self.last_plan = None
+
+    def _all_to_all(self, out, inp, out_splits=None, in_splits=None):
+        if self.P == 1:
+            out.copy_(inp)
+        else:
+            dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits,
+                                   group=self.group)
+        return out
+
+    def forward(self, hidden, topk_weights, topk_ids):
+        """hidden [T_local, H]; topk_ids [T_local, k] GLOBAL expert ids; returns [T_local, H] bf16."""
+        ops, P = self.ops, self.P
+        T, H = hidden.shape
+        k = topk_ids.shape[1]
+        dev = hidden.device
+
+        # 1. sort this rank's routed rows by global expert (= by destination rank, then expert)
+        m_glob, _, perm, inv_perm = ops.route(topk_ids, self.E)
+        send_counts = m_glob.reshape(P, self.e_local).to(torch.int64)
+
+        # 2. counts exchange, then ONE host read of all split sizes
+        recv_counts = torch.empty_like(send_counts)
+        self._all_to_all(recv_counts, send_counts)
+        sizes = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()
+        send_splits, recv_splits = sizes[0].tolist(), sizes[1].tolist()
+        n_send, n_recv = sum(send_splits), sum(recv_splits)
+        self.last_plan = {"send_splits": send_splits, "recv_splits": recv_splits}
+
+        # 3. payload exchange
+        received = []
+        for pay in ops.dispatch_payloads(hidden):
+            send_buf = ops.gather(pay, perm, div=k)
+            recv_buf = torch.empty((n_recv, pay.shape[1]), dtype=pay.dtype, device=dev)
+            received.append(self._all_to_all(recv_buf, send_buf, recv_splits, send_splits))
+
+        # 4. arrivals are ordered (source rank, expert); the GEMM wants (expert, source rank)
+        ids_recv = expert_ids_from_counts(recv_counts, n_recv)
+        m_loc, _, perm2, inv_perm2 = ops.route(ids_recv, self.e_local)
+        rows = [ops.gather(r, perm2) for r in received]
+
+        # 5. the experts
+        y = ops.expert_ffn(rows, m_loc)
+
+        # 6. back to arrival order and home
+        y_arrival = ops.gather(y, inv_perm2)
+        y_home = torch.empty((n_send, H), dtype=y.dtype, device=dev)
+        self._all_to_all(y_home, y_arrival, send_splits, recv_splits)
+
+        # 7. weighted sum over the top-k on the home rank
+        return ops.combine(y_home, inv_perm, topk_weights, T, k)
+
+    __call__ = forward

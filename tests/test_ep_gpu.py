@@ -1,0 +1,99 @@
+"""Expert-parallel layer on GPUs: the single-rank layer against the oracle and against
+fused_moe, and (when at least two GPUs are visible) two NCCL ranks against one."""
+import os
+import socket
+
+import pytest
+import torch
+
+import applied_ai_b200 as B
+from applied_ai_b200.ep import CudaOps, ExpertParallelMoE
+from oracle import grouped as O
+from tests.helpers import BF16_REL_TOL, FP8_REL_TOL
+
+pytestmark = pytest.mark.gpu
+
+
+def problem(T, H, I, E, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) * H ** -0.5).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * I ** -0.5).to(torch.bfloat16)
+    tw, ids = torch.topk(torch.softmax(torch.randn(T, E, generator=g), -1), k)
+    return hidden, w1, w2, tw, ids.to(torch.int32)
+
+
+def test_single_rank_bf16_equals_fused_moe():
+    hidden, w1, w2, tw, ids = problem(300, 256, 384, 8, 2, 1)
+    d = "cuda"
+    layer = ExpertParallelMoE(CudaOps(w1.to(d), w2.to(d), "bf16"), 8)
+    out = layer(hidden.to(d), tw.to(d), ids.to(d))
+    assert torch.equal(out, B.fused_moe(hidden.to(d), w1.to(d), w2.to(d), tw.to(d), ids.to(d)))
+    assert O.rel_err(out.cpu().float(), O.torch_moe_ref(hidden, w1, w2, tw, ids)) <= BF16_REL_TOL
+
+
+def fp8_layer_reference(hidden, ops, tw, ids):
+    """The layer on the same quantised operands: 1x128-quantised tokens, block-quantised
+    weights, intermediate rounded to bf16 and quantised 1x128 again before the down GEMM."""
+    E = ops.w1.shape[0]
+    xq, xs = O.quant_1x128_ref(hidden)
+    T, k = ids.shape
+    out = torch.zeros(T, ops.w2.shape[1])
+    w1, s1, w2, s2 = ops.w1.cpu(), ops.w1_scale.cpu(), ops.w2.cpu(), ops.w2_scale.cpu()
+    for e in range(E):
+        for j in range(k):
+            rows = torch.nonzero(ids[:, j] == e).reshape(-1)
+            if rows.numel() == 0:
+                continue
+            m = torch.tensor([rows.numel()], dtype=torch.int32)
+            h = O.silu_and_mul_ref(O.grouped_gemm_fp8_blockwise_ref(xq[rows], w1[e][None], m, xs[rows], s1[e][None]))
+            hq, hs = O.quant_1x128_ref(h.to(torch.bfloat16))
+            y = O.grouped_gemm_fp8_blockwise_ref(hq, w2[e][None], m, hs, s2[e][None]).to(torch.bfloat16).float()
+            out[rows] += tw[rows, j:j + 1].float() * y
+    return out
+
+
+def test_single_rank_fp8_blockwise_layer():
+    hidden, w1, w2, tw, ids = problem(200, 256, 256, 4, 2, 2)
+    d = "cuda"
+    ops = CudaOps(w1.to(d), w2.to(d), "fp8_blockwise")
+    out = ExpertParallelMoE(ops, 4)(hidden.to(d), tw.to(d), ids.to(d))
+    ref = fp8_layer_reference(hidden, ops, tw, ids)
+    assert O.rel_err(out.cpu().float(), ref) <= FP8_REL_TOL
+
+
+def _worker(rank, world, port, mode, ret):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    d = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=d)
+    try:
+        T, H, I, E, k = 512, 256, 256, 8, 2
+        hidden, w1, w2, tw, ids = problem(T, H, I, E, k, 3)
+        tl, el = T // world, E // world
+        sl = slice(rank * tl, (rank + 1) * tl)
+        ops = CudaOps(w1[rank * el:(rank + 1) * el].to(d), w2[rank * el:(rank + 1) * el].to(d), mode, cta_group=2)
+        out = ExpertParallelMoE(ops, E)(hidden[sl].to(d), tw[sl].to(d), ids[sl].to(d))
+        torch.cuda.synchronize()
+        ret[rank] = out.cpu()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("mode", ["bf16", "fp8_blockwise"])
+def test_two_ranks_equal_one_rank_bit_for_bit(mode):
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, port, mode, ret), nprocs=2, join=True)
+    hidden, w1, w2, tw, ids = problem(512, 256, 256, 8, 2, 3)
+    d = "cuda"
+    one = ExpertParallelMoE(CudaOps(w1.to(d), w2.to(d), mode, cta_group=2), 8)(hidden.to(d), tw.to(d), ids.to(d)).cpu()
+    two = torch.cat([ret[0], ret[1]])
+    assert torch.equal(one, two)
