@@ -53,9 +53,12 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Arrive on a barrier given by a shared::cluster address (own or peer CTA).
+// Arrive on a barrier given by a shared::cluster address (own or peer CTA).  Default
+// semantics (release at CTA scope): the barriers signalled this way order TMEM accesses,
+// which tcgen05.fence covers, not data in memory.  A cluster-scope release here was
+// measured at ~1300 cycles per arrive and dominated the block-wise FP8 kernel.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
