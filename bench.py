@@ -294,6 +294,7 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner off stdout
         dist.init_process_group("nccl", device_id=dev)
     _lib.load(build_if_missing=False)
     B.set_default_check(False)
@@ -433,6 +434,8 @@ LAYERS = {
     # name: (T tokens global, H, I, E, k, mode)
     "c3": (4096, 4096, 14336, 8, 2, "bf16"),            # Mixtral-8x7B FFN layer shapes, 1 GPU
     "c4": (32768, 7168, 2048, 256, 8, "fp8_blockwise"),  # DeepSeek-V3 routed-expert layer shapes, expert parallel
+    # what ONE rank computes in c4 at 8-way expert parallelism (32 experts, 32768 routed rows), without the exchange
+    "c4_rank8": (4096, 7168, 2048, 32, 8, "fp8_blockwise"),
 }
 
 
@@ -450,12 +453,13 @@ def run_layer(args):
     dev = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner off stdout
         dist.init_process_group("nccl", device_id=dev)
     _lib.load(build_if_missing=False)
     B.set_default_check(False)
     T, H, I, E, k, mode = LAYERS[args.workload]
-    if args.workload == "c3" and world > 1:
-        raise SystemExit("c3 is a single-GPU workload")
+    if args.workload in ("c3", "c4_rank8") and world > 1:
+        raise SystemExit(f"{args.workload} is a single-GPU workload")
     t_loc, e_loc = T // world, E // world
 
     # routing from one global seeded draw (identical on every rank), tokens and weights per owner
