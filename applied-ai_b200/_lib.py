@@ -38,11 +38,11 @@ STATUS_NAMES = {
 SIGNATURES = {
     "b200moe_version": [],
     "b200moe_grouped_gemm_bf16": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_i64, _c_i64,
-                                  _c_int, _c_int, _c_vp, _c_vp],
+                                  _c_int, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
     "b200moe_grouped_gemm_fp8_rowwise": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
-                                         _c_i64, _c_i64, _c_int, _c_vp, _c_vp],
+                                         _c_i64, _c_i64, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
     "b200moe_grouped_gemm_fp8_blockwise": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
-                                           _c_i64, _c_i64, _c_int, _c_int, _c_vp, _c_vp],
+                                           _c_i64, _c_i64, _c_int, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
     "b200moe_route_workspace_bytes": [_c_int, _c_int, ctypes.POINTER(_c_sz)],
     "b200moe_route": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp],
     "b200moe_route_noalloc": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp],

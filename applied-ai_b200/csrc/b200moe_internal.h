@@ -32,6 +32,8 @@ struct GGParams {
     const float* x_scale;
     const float* w_scale;
     int32_t* status;
+    const int32_t* row_map;        // optional: row r of the result is stored at row row_map[r] of y
+    int y_rows;                    // rows of y (bounds for row_map)
     long long ldy;                 // elements between consecutive rows of y
     long long y_col_group_stride;  // first column of group g's block is g * this (0: all groups share columns)
     int M, N, K, G;
@@ -47,6 +49,8 @@ struct GGLaunch {
     const float* x_scale;
     const float* w_scale;
     int32_t* status;
+    const int32_t* row_map;
+    int y_rows;
     long long ldy;
     long long y_col_group_stride;
     int M, N, K, G;

@@ -25,13 +25,15 @@ int b200moe_version(void) { return 1; }
 
 int b200moe_grouped_gemm_bf16(const void* x, const void* w, const int32_t* m_sizes, void* y, int M, int N, int K,
                               int G, int64_t ldy, int64_t y_col_group_stride, int epilogue, int cta_group,
-                              int32_t* status, b200moe_stream_t stream) {
+                              const int32_t* y_row_map, int y_rows, int32_t* status, b200moe_stream_t stream) {
     GGLaunch a{};
     a.x = x;
     a.w = w;
     a.m_sizes = m_sizes;
     a.y = y;
     a.status = status;
+    a.row_map = y_row_map;
+    a.y_rows = y_rows;
     a.ldy = ldy;
     a.y_col_group_stride = y_col_group_stride;
     a.M = M;
@@ -43,14 +45,14 @@ int b200moe_grouped_gemm_bf16(const void* x, const void* w, const int32_t* m_siz
     a.epilogue = epilogue;
     a.cta_group = cta_group;
     a.stream = static_cast<cudaStream_t>(stream);
-    if (ldy <= 0 || y_col_group_stride < 0) return kErrBadArgument;
+    if (ldy <= 0 || y_col_group_stride < 0 || (y_row_map != nullptr && y_rows <= 0)) return kErrBadArgument;
     return grouped_gemm_launch(a);
 }
 
 int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
                                      const int32_t* m_sizes, void* y, int M, int N, int K, int G, int64_t ldy,
-                                     int64_t y_col_group_stride, int cta_group, int32_t* status,
-                                     b200moe_stream_t stream) {
+                                     int64_t y_col_group_stride, int cta_group, const int32_t* y_row_map,
+                                     int y_rows, int32_t* status, b200moe_stream_t stream) {
     GGLaunch a{};
     a.x = xq;
     a.w = wq;
@@ -59,6 +61,8 @@ int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float
     a.x_scale = x_scale;
     a.w_scale = w_scale;
     a.status = status;
+    a.row_map = y_row_map;
+    a.y_rows = y_rows;
     a.ldy = ldy;
     a.y_col_group_stride = y_col_group_stride;
     a.M = M;
@@ -70,13 +74,14 @@ int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float
     a.epilogue = 0;
     a.cta_group = cta_group;
     a.stream = static_cast<cudaStream_t>(stream);
-    if (ldy <= 0 || y_col_group_stride < 0) return kErrBadArgument;
+    if (ldy <= 0 || y_col_group_stride < 0 || (y_row_map != nullptr && y_rows <= 0)) return kErrBadArgument;
     return grouped_gemm_launch(a);
 }
 
 int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
                                        const int32_t* m_sizes, void* y, int M, int N, int K, int G, int64_t ldy,
-                                       int64_t y_col_group_stride, int epilogue, int cta_group, int32_t* status,
+                                       int64_t y_col_group_stride, int epilogue, int cta_group,
+                                       const int32_t* y_row_map, int y_rows, int32_t* status,
                                        b200moe_stream_t stream) {
     GGLaunch a{};
     a.x = xq;
@@ -86,6 +91,8 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
     a.x_scale = x_scale;
     a.w_scale = w_scale;
     a.status = status;
+    a.row_map = y_row_map;
+    a.y_rows = y_rows;
     a.ldy = ldy;
     a.y_col_group_stride = y_col_group_stride;
     a.M = M;
@@ -97,7 +104,7 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
     a.epilogue = epilogue;
     a.cta_group = cta_group;
     a.stream = static_cast<cudaStream_t>(stream);
-    if (ldy <= 0 || y_col_group_stride < 0) return kErrBadArgument;
+    if (ldy <= 0 || y_col_group_stride < 0 || (y_row_map != nullptr && y_rows <= 0)) return kErrBadArgument;
     return grouped_gemm_fp8_block_launch(a);
 }
 

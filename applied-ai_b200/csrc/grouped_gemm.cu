@@ -153,8 +153,15 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 
             constexpr int kOutCols = EPI == 1 ? 128 : kTileN;  // output columns per tile
             const int col0 = tc.n_idx * kOutCols;              // first output column of the tile (within group)
-            __nv_bfloat16* const y_row =
-                y + static_cast<size_t>(row_ok ? row : 0) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
+            // Destination row: the row itself, or where the caller's row map sends it.
+            int drow = row;
+            bool store_ok = row_ok;
+            if (row_ok && p.row_map != nullptr) {
+                drow = __ldg(p.row_map + row);
+                store_ok = drow >= 0 && drow < p.y_rows;
+            }
+            __nv_bfloat16* const y_row = y + static_cast<size_t>(store_ok ? drow : 0) * p.ldy +
+                                         static_cast<size_t>(tc.g) * p.y_col_group_stride;
             const float* const w_scale_g = SCALE == 1 ? p.w_scale + static_cast<size_t>(tc.g) * p.N : nullptr;
 
 #pragma unroll 1
@@ -184,7 +191,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                         f[j] = f[j] * x_scale * ws;
                     }
                 }
-                if (row_ok) {
+                if (store_ok) {
                     __nv_bfloat16* dst = y_row + col;
                     const bool vec = (col + 32 <= p.n_out) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
                     if (vec) {
@@ -292,6 +299,8 @@ int grouped_gemm_launch(const GGLaunch& a) {
     p.x_scale = a.x_scale;
     p.w_scale = a.w_scale;
     p.status = a.status;
+    p.row_map = a.row_map;
+    p.y_rows = a.row_map ? a.y_rows : a.M;
     p.M = a.M;
     p.N = a.N;
     p.K = a.K;

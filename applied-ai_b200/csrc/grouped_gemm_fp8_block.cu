@@ -199,9 +199,15 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             if (!ok) break;
 
             // ---- store: the thread's row, its (up to) 128 output columns
-            if (row_ok) {
+            int drow = row;
+            bool store_ok = row_ok;
+            if (row_ok && p.row_map != nullptr) {
+                drow = __ldg(p.row_map + row);
+                store_ok = drow >= 0 && drow < p.y_rows;
+            }
+            if (store_ok) {
                 __nv_bfloat16* const y_row =
-                    y + static_cast<size_t>(row) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
+                    y + static_cast<size_t>(drow) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
                 if constexpr (EPI == 1) {
                     const int col = tc.n_idx * 128 + half * 64;  // 64 output columns: silu(gate) * up
 #pragma unroll
@@ -288,6 +294,8 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.x_scale = a.x_scale;
     p.w_scale = a.w_scale;
     p.status = a.status;
+    p.row_map = a.row_map;
+    p.y_rows = a.row_map ? a.y_rows : a.M;
     p.M = a.M;
     p.N = a.N;
     p.K = a.K;

@@ -349,51 +349,69 @@ int combine_topk_launch(const void* y, const int32_t* inv_perm, const float* wei
 
 // ------------------------------------------------------------------ 1x128 quantiser
 // For every run of 128 consecutive elements: scale = max(amax, 1e-12) / 448,
-// q = clamp(x / scale, +-448) rounded to e4m3 (nearest even).  One warp per run,
-// 4 elements per lane.  IEEE division, so results match the same formula evaluated
-// in fp32 on the host bit for bit.
+// q = clamp(x / scale, +-448) rounded to e4m3 (nearest even).  Sixteen lanes per run,
+// 8 elements (one 16-byte load for bf16) per lane, so a warp covers two runs at a time.
+// IEEE division, so results match the same formula evaluated in fp32 on the host bit for
+// bit.
 template <typename In>
 __global__ void __launch_bounds__(256)
 quant_1x128_kernel(const In* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scales, long long groups) {
     const int lane = threadIdx.x & 31;
-    const long long warps_total = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-    for (long long grp = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5); grp < groups;
-         grp += warps_total) {
-        const In* src = x + grp * 128 + lane * 4;
-        float f[4];
-        if constexpr (sizeof(In) == 2) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(src);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-            f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    const int sub = lane & 15;  // position inside the run
+    const long long halves_total = static_cast<long long>(gridDim.x) * (blockDim.x >> 4);
+    for (long long grp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 4;
+         grp < ((groups + 1) & ~1ll); grp += halves_total) {
+        const bool live = grp < groups;  // odd tail: the idle half-warp still joins the shuffles
+        float f[8];
+        if (live) {
+            const In* src = x + grp * 128 + sub * 8;
+            if constexpr (sizeof(In) == 2) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 a = __bfloat1622float2(h[j]);
+                    f[2 * j] = a.x;
+                    f[2 * j + 1] = a.y;
+                }
+            } else {
+                const float4 r0 = *reinterpret_cast<const float4*>(src);
+                const float4 r1 = *reinterpret_cast<const float4*>(src + 4);
+                f[0] = r0.x; f[1] = r0.y; f[2] = r0.z; f[3] = r0.w;
+                f[4] = r1.x; f[5] = r1.y; f[6] = r1.z; f[7] = r1.w;
+            }
         } else {
-            const float4 raw = *reinterpret_cast<const float4*>(src);
-            f[0] = raw.x; f[1] = raw.y; f[2] = raw.z; f[3] = raw.w;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = 0.0f;
         }
-        float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+        float amax = 0.0f;
 #pragma unroll
-        for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+#pragma unroll
+        for (int d = 8; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
         const float scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
-        uint32_t packed = 0;
+        uint32_t packed[2] = {0u, 0u};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 8; ++j) {
             float v = __fdiv_rn(f[j], scale);
             v = fminf(fmaxf(v, -448.0f), 448.0f);
             const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
-            packed |= static_cast<uint32_t>(b) << (8 * j);
+            packed[j >> 2] |= static_cast<uint32_t>(b) << (8 * (j & 3));
         }
-        *reinterpret_cast<uint32_t*>(q + grp * 128 + lane * 4) = packed;
-        if (lane == 0) scales[grp] = scale;
+        if (live) {
+            *reinterpret_cast<uint2*>(q + grp * 128 + sub * 8) = make_uint2(packed[0], packed[1]);
+            if (sub == 0) scales[grp] = scale;
+        }
     }
 }
 
 int quant_1x128_launch(const void* x, int x_is_fp32, void* q, float* scales, long long rows, int K,
                        cudaStream_t stream) {
     if (rows < 0 || K <= 0 || (K % 128) != 0) return kErrBadArgument;
-    if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(q) & 3u)) return kErrAlignment;
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(q) & 7u)) return kErrAlignment;
     const long long groups = rows * (K / 128);
     if (groups == 0) return 0;
-    long long blocks = (groups + 7) / 8;
+    long long blocks = (groups + 15) / 16;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (x_is_fp32)
         quant_1x128_kernel<float><<<static_cast<int>(blocks), 256, 0, stream>>>(

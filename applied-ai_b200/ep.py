@@ -4,7 +4,7 @@ Rank r of P owns experts [r*E/P, (r+1)*E/P) and T/P tokens.  One exchange each w
 
     route by global expert  ->  counts all-to-all  ->  payload all-to-all (rows sorted by
     destination rank, then expert)  ->  re-sort arrivals by local expert  ->  grouped GEMM
-    (gate+up, SwiGLU)  ->  grouped GEMM (down)  ->  back to arrival order  ->  return
+    (gate+up, SwiGLU)  ->  grouped GEMM (down, stored back in arrival order)  ->  return
     all-to-all  ->  weighted top-k combine on the home rank
 
 The reference has no distributed code at all (`fused_moe` assumes every expert is local,
@@ -64,18 +64,21 @@ class CudaOps:
         q, s = self._quant.float8_groupwise_quantize(hidden)
         return [q.view(torch.uint8), s]
 
-    def expert_ffn(self, rows, m_sizes):
-        """rows: payload tensors sorted by local expert -> [R, H] bf16."""
+    def expert_ffn(self, rows, m_sizes, out_row_map=None):
+        """rows: payload tensors sorted by local expert -> [R, H] bf16.  With out_row_map the
+        down GEMM stores sorted row r at row out_row_map[r] (leaving expert order in the
+        same pass)."""
         gg = self._gg
         if self.mode == "bf16":
             h = gg.grouped_gemm(rows[0], self.w1, m_sizes, epilogue="swiglu", check=False, cta_group=self.cta_group)
-            return gg.grouped_gemm(h, self.w2, m_sizes, check=False, cta_group=self.cta_group)
+            return gg.grouped_gemm(h, self.w2, m_sizes, check=False, cta_group=self.cta_group,
+                                   out_row_map=out_row_map)
         xq, xs = rows[0].view(torch.float8_e4m3fn), rows[1]
         h = gg.grouped_gemm_fp8_blockwise(xq, self.w1, m_sizes, xs, self.w1_scale, epilogue="swiglu", check=False,
                                           cta_group=self.cta_group)
         hq, hs = self._quant.float8_groupwise_quantize(h)
         return gg.grouped_gemm_fp8_blockwise(hq, self.w2, m_sizes, hs, self.w2_scale, check=False,
-                                             cta_group=self.cta_group)
+                                             cta_group=self.cta_group, out_row_map=out_row_map)
 
     def combine(self, y, inv_perm, topk_weights, num_tokens, top_k):
         return self._moe.combine_topk(y, inv_perm, topk_weights, num_tokens, top_k)
@@ -127,6 +130,13 @@ class ExpertParallelMoE:
         m_glob, _, perm, inv_perm = ops.route(topk_ids, self.E)
         send_counts = m_glob.reshape(P, self.e_local).to(torch.int64)
 
+        if P == 1:
+            # every expert is local: the routed order already is the expert order
+            rows = [ops.gather(pay, perm, div=k) for pay in ops.dispatch_payloads(hidden)]
+            y_home = ops.expert_ffn(rows, m_glob)
+            self.last_plan = {"send_splits": [int(topk_ids.numel())], "recv_splits": [int(topk_ids.numel())]}
+            return ops.combine(y_home, inv_perm, topk_weights, T, k)
+
         # 2. counts exchange, then ONE host read of all split sizes
         recv_counts = torch.empty_like(send_counts)
         self._all_to_all(recv_counts, send_counts)
@@ -144,15 +154,14 @@ class ExpertParallelMoE:
 
         # 4. arrivals are ordered (source rank, expert); the GEMM wants (expert, source rank)
         ids_recv = expert_ids_from_counts(recv_counts, n_recv)
-        m_loc, _, perm2, inv_perm2 = ops.route(ids_recv, self.e_local)
+        m_loc, _, perm2, _ = ops.route(ids_recv, self.e_local)
         rows = [ops.gather(r, perm2) for r in received]
 
-        # 5. the experts
-        y = ops.expert_ffn(rows, m_loc)
+        # 5. the experts; the down GEMM stores each row straight back at its arrival position
+        y_arrival = ops.expert_ffn(rows, m_loc, out_row_map=perm2)
 
-        # 6. back to arrival order and home
-        y_arrival = ops.gather(y, inv_perm2)
-        y_home = torch.empty((n_send, H), dtype=y.dtype, device=dev)
+        # 6. home
+        y_home = torch.empty((n_send, H), dtype=y_arrival.dtype, device=dev)
         self._all_to_all(y_home, y_arrival, send_splits, recv_splits)
 
         # 7. weighted sum over the top-k on the home rank

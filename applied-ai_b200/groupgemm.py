@@ -86,23 +86,38 @@ def _prepare(x, w, m_sizes, elem_dtype):
     return m_sizes, G, M, N, K
 
 
-def _launch_bf16(x, w, m_sizes, y, M, N, K, G, ldy, col_stride, epilogue, cta_group, check, what):
+def _row_map_args(out_row_map, y, device):
+    """(pointer, rows of y) for the optional output row map."""
+    if out_row_map is None:
+        return 0, 0
+    _require(isinstance(out_row_map, torch.Tensor) and out_row_map.device == device and
+             out_row_map.dtype == torch.int32 and out_row_map.is_contiguous(),
+             "out_row_map must be a contiguous int32 tensor on the same device")
+    return out_row_map.data_ptr(), y.shape[0]
+
+
+def _launch_bf16(x, w, m_sizes, y, M, N, K, G, ldy, col_stride, epilogue, cta_group, check, what, out_row_map=None):
     lib = _lib.load()
     word = _status_word(x.device)
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream().cuda_stream
+        map_ptr, y_rows = _row_map_args(out_row_map, y, x.device)
         rc = lib.b200moe_grouped_gemm_bf16(x.data_ptr(), w.data_ptr(), m_sizes.data_ptr(), y.data_ptr(), M, N, K, G,
-                                           ldy, col_stride, epilogue, cta_group, word.data_ptr(), stream)
+                                           ldy, col_stride, epilogue, cta_group, map_ptr, y_rows, word.data_ptr(),
+                                           stream)
     _lib.check(rc, what)
     if _default_check if check is None else check:
         raise_on_status(word, what)
 
 
-def grouped_gemm(x, w, m_sizes, *, epilogue="none", cta_group=0, check=None):
+def grouped_gemm(x, w, m_sizes, *, epilogue="none", cta_group=0, check=None, out_row_map=None, out_rows=None):
     """y[rows of group g] = x[rows of group g] @ w[g].T, bf16 in, fp32 accumulate, bf16 out.
 
     epilogue="swiglu": w[g] is [gate; up] (N = 2*I rows) and y gets I columns,
     silu(gate) * up computed on the fp32 accumulators.
+    out_row_map (int32 [M], optional): row r of the result is stored at row out_row_map[r]
+    of the output, which then has out_rows rows (default M); rows no entry points to stay
+    unwritten.
     """
     m_sizes, G, M, N, K = _prepare(x, w, m_sizes, torch.bfloat16)
     epi = {"none": 0, "swiglu": 1}.get(epilogue)
@@ -110,9 +125,9 @@ def grouped_gemm(x, w, m_sizes, *, epilogue="none", cta_group=0, check=None):
     if epi == 1:
         _require(N % 2 == 0, "SwiGLU needs an even number of weight rows per group")
     n_out = N // 2 if epi == 1 else N
-    y = torch.empty((M, n_out), device=x.device, dtype=torch.bfloat16)
+    y = torch.empty((M if out_rows is None else out_rows, n_out), device=x.device, dtype=torch.bfloat16)
     if M > 0:
-        _launch_bf16(x, w, m_sizes, y, M, N, K, G, n_out, 0, epi, cta_group, check, "grouped_gemm")
+        _launch_bf16(x, w, m_sizes, y, M, N, K, G, n_out, 0, epi, cta_group, check, "grouped_gemm", out_row_map)
     return y
 
 
@@ -140,19 +155,21 @@ def grouped_gemm_fp8_rowwise(x, w, m_sizes, x_scale, w_scale, *, cta_group=0, ch
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.b200moe_grouped_gemm_fp8_rowwise(x.data_ptr(), w.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
                                                   m_sizes.data_ptr(), y.data_ptr(), M, N, K, G, N, 0, cta_group,
-                                                  word.data_ptr(), stream)
+                                                  0, 0, word.data_ptr(), stream)
     _lib.check(rc, "grouped_gemm_fp8_rowwise")
     if _default_check if check is None else check:
         raise_on_status(word, "grouped_gemm_fp8_rowwise")
     return y
 
 
-def grouped_gemm_fp8_blockwise(x, w, m_sizes, x_scale, w_scale, *, epilogue="none", cta_group=0, check=None):
+def grouped_gemm_fp8_blockwise(x, w, m_sizes, x_scale, w_scale, *, epilogue="none", cta_group=0, check=None,
+                               out_row_map=None, out_rows=None):
     """FP8 grouped GEMM with 1x128 activation scales and 128x128 weight-block scales -> bf16.
 
     x [M, K], w [G*N, K] or [G, N, K] float8_e4m3fn; x_scale [M, K/128] fp32 (as produced by
     float8_groupwise_quantize); w_scale [G, ceil(N/128), K/128] fp32 (quantize_fp8_block).
-    epilogue="swiglu": w[g] = [gate; up], output has N/2 columns."""
+    epilogue="swiglu": w[g] = [gate; up], output has N/2 columns.  out_row_map / out_rows as in
+    grouped_gemm."""
     m_sizes, G, M, N, K = _prepare(x, w, m_sizes, torch.float8_e4m3fn)
     _require(K % 128 == 0, "K must be a multiple of 128 for block-wise scales")
     epi = {"none": 0, "swiglu": 1}.get(epilogue)
@@ -167,16 +184,17 @@ def grouped_gemm_fp8_blockwise(x, w, m_sizes, x_scale, w_scale, *, epilogue="non
     _require(tuple(x_scale.shape) == (M, K // 128), f"x_scale must be [M, K/128] = [{M}, {K // 128}]")
     _require(w_scale.numel() == G * nblk * (K // 128), f"w_scale must be [G, ceil(N/128), K/128] = [{G}, {nblk}, {K // 128}]")
     n_out = N // 2 if epi == 1 else N
-    y = torch.empty((M, n_out), device=x.device, dtype=torch.bfloat16)
+    y = torch.empty((M if out_rows is None else out_rows, n_out), device=x.device, dtype=torch.bfloat16)
     if M == 0:
         return y
     lib = _lib.load()
     word = _status_word(x.device)
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream().cuda_stream
+        map_ptr, y_rows = _row_map_args(out_row_map, y, x.device)
         rc = lib.b200moe_grouped_gemm_fp8_blockwise(x.data_ptr(), w.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
                                                     m_sizes.data_ptr(), y.data_ptr(), M, N, K, G, n_out, 0, epi,
-                                                    cta_group, word.data_ptr(), stream)
+                                                    cta_group, map_ptr, y_rows, word.data_ptr(), stream)
     _lib.check(rc, "grouped_gemm_fp8_blockwise")
     if _default_check if check is None else check:
         raise_on_status(word, "grouped_gemm_fp8_blockwise")

@@ -35,7 +35,7 @@ def grouped_gemm_fp8_rowwise(x, w, m_sizes, x_scale, w_scale, *, zero_fill=False
         stream = torch.cuda.current_stream().cuda_stream
         rc = lib.b200moe_grouped_gemm_fp8_rowwise(x.data_ptr(), w.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
                                                   m_sizes.data_ptr(), y.data_ptr(), M, N, K, G, N * G, N, cta_group,
-                                                  word.data_ptr(), stream)
+                                                  0, 0, word.data_ptr(), stream)
     _lib.check(rc, "grouped_gemm_fp8_rowwise")
     if _gg._default_check if check is None else check:
         _gg.raise_on_status(word, "grouped_gemm_fp8_rowwise")

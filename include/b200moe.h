@@ -56,10 +56,15 @@ int b200moe_version(void);
  * y_col_group_stride = N, ldy = N*G gives the [M, N*G] block layout of
  *   grouped_gemm_forward(x, w, m_sizes)    kernels/MoE/group_GEMM/triton/tgroup_gemm_forward.py:626 (-> :485).
  * With B200MOE_EPI_SWIGLU the activation of v0_moe_fused.py:284 (silu_and_mul) is
- * applied to the accumulators and y has N/2 columns per group. */
+ * applied to the accumulators and y has N/2 columns per group.
+ * y_row_map (device, may be NULL): when given, row r of the result is stored at row
+ * y_row_map[r] of y (y has y_rows rows; entries outside [0, y_rows) are skipped).  This
+ * is the scatter the reference's GEMM does through sorted_token_ids
+ * (v0_moe_fused.py:132-135), used here to leave expert-sorted order in the same pass.
+ * The FP8 entry points take the same two arguments. */
 int b200moe_grouped_gemm_bf16(const void* x, const void* w, const int32_t* m_sizes, void* y, int M, int N, int K,
                               int G, int64_t ldy, int64_t y_col_group_stride, int epilogue, int cta_group,
-                              int32_t* status, b200moe_stream_t stream);
+                              const int32_t* y_row_map, int y_rows, int32_t* status, b200moe_stream_t stream);
 
 /* Row-wise scaled FP8: y = (xq @ wq[g]^T) * x_scale[row] * w_scale[g*N + col].
  * xq [M,K], wq [G,N,K] float8_e4m3fn; x_scale [M] fp32; w_scale [G*N] fp32; y bf16.
@@ -67,8 +72,8 @@ int b200moe_grouped_gemm_bf16(const void* x, const void* w, const int32_t* m_siz
  *   dev/triton_groupGEMM/groupgemm.py:524, kernels/MoE/group_GEMM/triton/tgroup_gemm_forward.py:632. */
 int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
                                      const int32_t* m_sizes, void* y, int M, int N, int K, int G, int64_t ldy,
-                                     int64_t y_col_group_stride, int cta_group, int32_t* status,
-                                     b200moe_stream_t stream);
+                                     int64_t y_col_group_stride, int cta_group, const int32_t* y_row_map,
+                                     int y_rows, int32_t* status, b200moe_stream_t stream);
 
 /* Block-wise scaled FP8 (1x128 activation scales, 128x128 weight scales):
  *   y[m,n] = sum_kb (xq[m, kb*128:(kb+1)*128] . wq[g][n, same]) * x_scale[m, kb] * w_scale[g][n/128][kb]
@@ -79,7 +84,8 @@ int b200moe_grouped_gemm_fp8_rowwise(const void* xq, const void* wq, const float
  * the activation-scale convention is float8_groupwise_quant.py:36-46. */
 int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
                                        const int32_t* m_sizes, void* y, int M, int N, int K, int G, int64_t ldy,
-                                       int64_t y_col_group_stride, int epilogue, int cta_group, int32_t* status,
+                                       int64_t y_col_group_stride, int epilogue, int cta_group,
+                                       const int32_t* y_row_map, int y_rows, int32_t* status,
                                        b200moe_stream_t stream);
 
 /* Routing: stable counting sort of ids[R] (R = tokens*top_k, flat index t*top_k + j)

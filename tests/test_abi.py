@@ -46,7 +46,7 @@ def test_argument_errors_need_no_device():
     assert lib.b200moe_route_workspace_bytes(10, 2048, ctypes.byref(n)) == 0
     assert lib.b200moe_route_workspace_bytes(10, 2049, ctypes.byref(n)) == -1
     # null pointers / bad sizes are rejected before any CUDA call
-    assert lib.b200moe_grouped_gemm_bf16(None, None, None, None, 8, 8, 8, 1, 8, 0, 0, 0, None, None) == -1
+    assert lib.b200moe_grouped_gemm_bf16(None, None, None, None, 8, 8, 8, 1, 8, 0, 0, 0, None, 0, None, None) == -1
     assert lib.b200moe_swiglu(None, None, 4, 8, None) == -1
     assert lib.b200moe_quant_1x128(None, 0, None, None, 4, 100, None) == -1
 

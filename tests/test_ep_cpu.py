@@ -32,12 +32,17 @@ class CpuRefOps:
         q, s = O.quant_1x128_ref(hidden)
         return [q.view(torch.uint8), s]
 
-    def expert_ffn(self, rows, m_sizes):
+    def expert_ffn(self, rows, m_sizes, out_row_map=None):
         x = rows[0]
         if self.two_part:
             x = rows[0].view(torch.float8_e4m3fn).float() * rows[1].repeat_interleave(128, dim=1)
         h = O.silu_and_mul_ref(O.grouped_gemm_ref(x, self.w1, m_sizes))
-        return O.grouped_gemm_ref(h, self.w2, m_sizes)
+        y = O.grouped_gemm_ref(h, self.w2, m_sizes)
+        if out_row_map is None:
+            return y
+        out = torch.empty_like(y)
+        out[out_row_map.long()] = y
+        return out
 
     def combine(self, y, inv_perm, topk_weights, num_tokens, top_k):
         return (y[inv_perm.long()].view(num_tokens, top_k, -1) * topk_weights.float().view(num_tokens, top_k, 1)).sum(1)
