@@ -64,20 +64,22 @@ class CudaOps:
         q, s = self._quant.float8_groupwise_quantize(hidden)
         return [q.view(torch.uint8), s]
 
-    def expert_ffn(self, rows, m_sizes, out_row_map=None):
+    def expert_ffn(self, rows, m_sizes, out_row_map=None, experts=None):
         """rows: payload tensors sorted by local expert -> [R, H] bf16.  With out_row_map the
         down GEMM stores sorted row r at row out_row_map[r] (leaving expert order in the
-        same pass)."""
+        same pass).  experts=(lo, hi) restricts the call to that range of local experts."""
         gg = self._gg
+        lo, hi = experts if experts is not None else (0, self.w1.shape[0])
         if self.mode == "bf16":
-            h = gg.grouped_gemm(rows[0], self.w1, m_sizes, epilogue="swiglu", check=False, cta_group=self.cta_group)
-            return gg.grouped_gemm(h, self.w2, m_sizes, check=False, cta_group=self.cta_group,
+            h = gg.grouped_gemm(rows[0], self.w1[lo:hi], m_sizes, epilogue="swiglu", check=False,
+                                cta_group=self.cta_group)
+            return gg.grouped_gemm(h, self.w2[lo:hi], m_sizes, check=False, cta_group=self.cta_group,
                                    out_row_map=out_row_map)
         xq, xs = rows[0].view(torch.float8_e4m3fn), rows[1]
-        h = gg.grouped_gemm_fp8_blockwise(xq, self.w1, m_sizes, xs, self.w1_scale, epilogue="swiglu", check=False,
-                                          cta_group=self.cta_group)
+        h = gg.grouped_gemm_fp8_blockwise(xq, self.w1[lo:hi], m_sizes, xs, self.w1_scale[lo:hi], epilogue="swiglu",
+                                          check=False, cta_group=self.cta_group)
         hq, hs = self._quant.float8_groupwise_quantize(h)
-        return gg.grouped_gemm_fp8_blockwise(hq, self.w2, m_sizes, hs, self.w2_scale, check=False,
+        return gg.grouped_gemm_fp8_blockwise(hq, self.w2[lo:hi], m_sizes, hs, self.w2_scale[lo:hi], check=False,
                                              cta_group=self.cta_group, out_row_map=out_row_map)
 
     def combine(self, y, inv_perm, topk_weights, num_tokens, top_k):
@@ -99,9 +101,13 @@ class ExpertParallelMoE:
     num_experts  global expert count E (divisible by the group size)
     group        torch.distributed process group (None: default group, or no exchange at
                  all when torch.distributed is not initialised — the single-GPU case)
+    waves        the local experts are cut into this many consecutive chunks; each chunk has
+                 its own dispatch and return all-to-all, issued asynchronously, so the
+                 exchange of one chunk runs under the GEMMs of its neighbours.  Must divide
+                 E / P (it is lowered to the nearest divisor otherwise).
     """
 
-    def __init__(self, ops, num_experts, group=None):
+    def __init__(self, ops, num_experts, group=None, waves=1):
         self.ops = ops
         self.group = group
         self.E = int(num_experts)
@@ -109,62 +115,93 @@ class ExpertParallelMoE:
         if self.E % self.P:
             raise ValueError(f"{self.E} experts cannot be split evenly over {self.P} ranks")
         self.e_local = self.E // self.P
+        waves = max(1, min(int(waves), self.e_local))
+        while self.e_local % waves:
+            waves -= 1
+        self.W = waves
+        self.e_wave = self.e_local // self.W
         self.last_plan = None
+        self._remap = None
 
-    def _all_to_all(self, out, inp, out_splits=None, in_splits=None):
-        if self.P == 1:
-            out.copy_(inp)
-        else:
-            dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits,
-                                   group=self.group)
-        return out
+    def _key_table(self, device):
+        """Sort key of every global expert: (wave, destination rank, expert inside the wave), so
+        that the rows of one wave are contiguous and, inside it, grouped by destination."""
+        if self._remap is None or self._remap.device != device:
+            e = torch.arange(self.E, device=device)
+            dest, el = e // self.e_local, e % self.e_local
+            wave, ew = el // self.e_wave, el % self.e_wave
+            self._remap = (wave * (self.P * self.e_wave) + dest * self.e_wave + ew).to(torch.int32)
+        return self._remap
+
+    def _a2a(self, out, inp, out_splits, in_splits):
+        return dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits,
+                                      group=self.group, async_op=True)
 
     def forward(self, hidden, topk_weights, topk_ids):
         """hidden [T_local, H]; topk_ids [T_local, k] GLOBAL expert ids; returns [T_local, H] bf16."""
-        ops, P = self.ops, self.P
+        ops, P, W, ew = self.ops, self.P, self.W, self.e_wave
         T, H = hidden.shape
         k = topk_ids.shape[1]
         dev = hidden.device
 
-        # 1. sort this rank's routed rows by global expert (= by destination rank, then expert)
-        m_glob, _, perm, inv_perm = ops.route(topk_ids, self.E)
-        send_counts = m_glob.reshape(P, self.e_local).to(torch.int64)
-
         if P == 1:
             # every expert is local: the routed order already is the expert order
+            m_glob, _, perm, inv_perm = ops.route(topk_ids, self.E)
             rows = [ops.gather(pay, perm, div=k) for pay in ops.dispatch_payloads(hidden)]
             y_home = ops.expert_ffn(rows, m_glob)
             self.last_plan = {"send_splits": [int(topk_ids.numel())], "recv_splits": [int(topk_ids.numel())]}
             return ops.combine(y_home, inv_perm, topk_weights, T, k)
 
+        # 1. sort this rank's routed rows by (wave, destination rank, expert)
+        keys = self._key_table(dev)[topk_ids.reshape(-1).long()]
+        m_key, _, perm, inv_perm = ops.route(keys, W * P * ew)
+        send_counts = m_key.reshape(W, P, ew).permute(1, 0, 2).contiguous().to(torch.int64)   # [dest, wave, expert]
+
         # 2. counts exchange, then ONE host read of all split sizes
-        recv_counts = torch.empty_like(send_counts)
-        self._all_to_all(recv_counts, send_counts)
-        sizes = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()
-        send_splits, recv_splits = sizes[0].tolist(), sizes[1].tolist()
-        n_send, n_recv = sum(send_splits), sum(recv_splits)
-        self.last_plan = {"send_splits": send_splits, "recv_splits": recv_splits}
+        recv_counts = torch.empty_like(send_counts)                                            # [src, wave, expert]
+        self._a2a(recv_counts, send_counts, None, None).wait()
+        sizes = torch.stack([send_counts.sum(2), recv_counts.sum(2)]).cpu()                    # [2, P, W]
+        send_pw, recv_pw = sizes[0], sizes[1]
+        n_send = int(send_pw.sum())
+        send_off = [0]
+        for w in range(W):
+            send_off.append(send_off[-1] + int(send_pw[:, w].sum()))
+        self.last_plan = {"send_splits": send_pw.sum(1).tolist(), "recv_splits": recv_pw.sum(1).tolist(),
+                          "waves": W}
 
-        # 3. payload exchange
-        received = []
-        for pay in ops.dispatch_payloads(hidden):
-            send_buf = ops.gather(pay, perm, div=k)
-            recv_buf = torch.empty((n_recv, pay.shape[1]), dtype=pay.dtype, device=dev)
-            received.append(self._all_to_all(recv_buf, send_buf, recv_splits, send_splits))
+        # 3. dispatch: every wave's payload all-to-all is issued now, in wave order
+        send_bufs = [ops.gather(pay, perm, div=k) for pay in ops.dispatch_payloads(hidden)]
+        pending = []
+        for w in range(W):
+            in_splits, out_splits = send_pw[:, w].tolist(), recv_pw[:, w].tolist()
+            n_recv = sum(out_splits)
+            bufs, works = [], []
+            for sb in send_bufs:
+                rb = torch.empty((n_recv, sb.shape[1]), dtype=sb.dtype, device=dev)
+                works.append(self._a2a(rb, sb[send_off[w]:send_off[w + 1]], out_splits, in_splits))
+                bufs.append(rb)
+            pending.append((bufs, works, n_recv, in_splits, out_splits))
 
-        # 4. arrivals are ordered (source rank, expert); the GEMM wants (expert, source rank)
-        ids_recv = expert_ids_from_counts(recv_counts, n_recv)
-        m_loc, _, perm2, _ = ops.route(ids_recv, self.e_local)
-        rows = [ops.gather(r, perm2) for r in received]
+        # 4. per wave: wait for its rows, sort arrivals by expert, run the experts, send results home
+        y_home = None
+        returns = []
+        for w, (bufs, works, n_recv, in_splits, out_splits) in enumerate(pending):
+            for wk in works:
+                wk.wait()
+            # arrivals are ordered (source rank, expert); the GEMM wants (expert, source rank)
+            ids_recv = expert_ids_from_counts(recv_counts[:, w, :], n_recv)
+            m_loc, _, perm2, _ = ops.route(ids_recv, ew)
+            rows = [ops.gather(r, perm2) for r in bufs]
+            # the down GEMM stores each row straight back at its arrival position
+            y_arrival = ops.expert_ffn(rows, m_loc, out_row_map=perm2, experts=(w * ew, (w + 1) * ew))
+            if y_home is None:
+                y_home = torch.empty((n_send, H), dtype=y_arrival.dtype, device=dev)
+            returns.append((self._a2a(y_home[send_off[w]:send_off[w + 1]], y_arrival, in_splits, out_splits),
+                            y_arrival))
 
-        # 5. the experts; the down GEMM stores each row straight back at its arrival position
-        y_arrival = ops.expert_ffn(rows, m_loc, out_row_map=perm2)
-
-        # 6. home
-        y_home = torch.empty((n_send, H), dtype=y_arrival.dtype, device=dev)
-        self._all_to_all(y_home, y_arrival, send_splits, recv_splits)
-
-        # 7. weighted sum over the top-k on the home rank
+        # 5. weighted sum over the top-k on the home rank
+        for wk, _ in returns:
+            wk.wait()
         return ops.combine(y_home, inv_perm, topk_weights, T, k)
 
     __call__ = forward

@@ -478,7 +478,7 @@ def run_layer(args):
     ops = CudaOps(w1, w2, mode=mode, cta_group=args.cta_group)
     if mode != "bf16":
         del w1, w2
-    layer = ExpertParallelMoE(ops, E)
+    layer = ExpertParallelMoE(ops, E, waves=args.waves)
 
     def step(h=hidden):
         return layer(h, topk_w, topk_ids)
@@ -596,7 +596,7 @@ def run_layer(args):
             "config": {"workload": f"{args.workload}: MoE FFN layer T={T} H={H} I={I} E={E} top-{k} {mode}, "
                                    f"{t_loc} tokens and {e_loc} experts per GPU",
                        "l2": "weights per GPU exceed the 126 MiB L2",
-                       "exchange": "NCCL all_to_all_single (counts, payload, return)" if world > 1 else "none (1 GPU)"},
+                       "exchange": f"NCCL all_to_all_single (counts, payload, return), {layer.W} waves" if world > 1 else "none (1 GPU)"},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
                          "frac": per_gpu / peak, "traffic": args.traffic, "peak_source": src,
                          "note": "whole layer (route, gather, 2 GEMMs, quantise, combine, exchange) against the GEMM peak"},
@@ -623,6 +623,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(LAYERS))
     ap.add_argument("--cta-group", type=int, default=0, dest="cta_group")
+    ap.add_argument("--waves", type=int, default=2,
+                    help="expert-parallel layers: chunks of local experts whose exchange overlaps compute")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture, echoed into the roofline object")
     args = ap.parse_args()

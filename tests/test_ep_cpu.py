@@ -32,12 +32,13 @@ class CpuRefOps:
         q, s = O.quant_1x128_ref(hidden)
         return [q.view(torch.uint8), s]
 
-    def expert_ffn(self, rows, m_sizes, out_row_map=None):
+    def expert_ffn(self, rows, m_sizes, out_row_map=None, experts=None):
+        lo, hi = experts if experts is not None else (0, self.w1.shape[0])
         x = rows[0]
         if self.two_part:
             x = rows[0].view(torch.float8_e4m3fn).float() * rows[1].repeat_interleave(128, dim=1)
-        h = O.silu_and_mul_ref(O.grouped_gemm_ref(x, self.w1, m_sizes))
-        y = O.grouped_gemm_ref(h, self.w2, m_sizes)
+        h = O.silu_and_mul_ref(O.grouped_gemm_ref(x, self.w1[lo:hi], m_sizes))
+        y = O.grouped_gemm_ref(h, self.w2[lo:hi], m_sizes)
         if out_row_map is None:
             return y
         out = torch.empty_like(y)
@@ -60,7 +61,7 @@ def make_problem(T, H, I, E, k, seed):
     return hidden, w1, w2, tw, ids.to(torch.int32)
 
 
-def _worker(rank, world, port, two_part, results):
+def _worker(rank, world, port, two_part, waves, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -69,7 +70,7 @@ def _worker(rank, world, port, two_part, results):
         t_loc, e_loc = T // world, E // world
         sl = slice(rank * t_loc, (rank + 1) * t_loc)
         ops = CpuRefOps(w1[rank * e_loc:(rank + 1) * e_loc], w2[rank * e_loc:(rank + 1) * e_loc], two_part)
-        layer = ExpertParallelMoE(ops, E)
+        layer = ExpertParallelMoE(ops, E, waves=waves)
         out = layer(hidden[sl], tw[sl], ids[sl])
         hid_ref = hidden
         if two_part:
@@ -89,11 +90,11 @@ def _free_port():
     return port
 
 
-@pytest.mark.parametrize("world,two_part", [(2, False), (2, True), (4, False)])
-def test_expert_parallel_matches_unsharded_layer(world, two_part):
+@pytest.mark.parametrize("world,two_part,waves", [(2, False, 1), (2, True, 2), (4, False, 2), (2, False, 4)])
+def test_expert_parallel_matches_unsharded_layer(world, two_part, waves):
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), two_part, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), two_part, waves, results), nprocs=world, join=True)
     assert len(results) == world
     sent = 0
     for r in range(world):
