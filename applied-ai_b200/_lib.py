@@ -30,6 +30,7 @@ STATUS_NAMES = {
     17: "device-side wait ran out (MMA issuer, operand stage)",
     18: "device-side wait ran out (MMA issuer, accumulator)",
     19: "device-side wait ran out (epilogue)",
+    20: "self-test wait ran out (expected)",
     32: "kernel image not built for sm_100a",
 }
 
@@ -43,9 +44,12 @@ SIGNATURES = {
                                          _c_i64, _c_i64, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
     "b200moe_grouped_gemm_fp8_blockwise": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
                                            _c_i64, _c_i64, _c_int, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
+    "b200moe_selftest_wait_timeout": [ctypes.c_uint64, _c_vp, _c_vp],
     "b200moe_route_workspace_bytes": [_c_int, _c_int, ctypes.POINTER(_c_sz)],
     "b200moe_route": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp],
     "b200moe_route_noalloc": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp],
+    "b200moe_moe_align_workspace_bytes": [_c_int, _c_int, ctypes.POINTER(_c_sz)],
+    "b200moe_moe_align_block_size": [_c_vp, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp],
     "b200moe_gather_rows": [_c_vp, _c_vp, _c_int, _c_vp, _c_int, _c_i64, _c_int, _c_vp],
     "b200moe_swiglu": [_c_vp, _c_vp, _c_i64, _c_int, _c_vp],
     "b200moe_combine_topk": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],

@@ -12,6 +12,7 @@ enum : int32_t {
     kStatusTimeoutMmaFull = 17,   // MMA issuer gave up waiting for a filled stage
     kStatusTimeoutMmaAcc = 18,    // MMA issuer gave up waiting for a drained accumulator
     kStatusTimeoutEpilogue = 19,  // epilogue gave up waiting for a finished accumulator
+    kStatusSelfTestTimeout = 20,  // the self-test's deliberately unsatisfied wait ran out (expected)
     kStatusWrongArch = 32,        // kernel image was not built for sm_100a
 };
 
@@ -62,6 +63,7 @@ struct GGLaunch {
 };
 
 int grouped_gemm_launch(const GGLaunch& a);
+int selftest_wait_launch(uint64_t limit_ns, int32_t* status, cudaStream_t stream);
 // FP8 with 1x128 activation scales [M, K/128] and 128x128 weight scales [G, ceil(N/128), K/128].
 int grouped_gemm_fp8_block_launch(const GGLaunch& a);
 

@@ -16,7 +16,7 @@ static_assert(B200MOE_EBADARG == kErrBadArgument && B200MOE_EALIGN == kErrAlignm
                   B200MOE_ETOOLARGE == kErrTooLarge,
               "public and internal error codes must agree");
 static_assert(B200MOE_SBADSIZES == kStatusBadGroupSizes && B200MOE_STIMEOUT_FIRST == kStatusTimeoutProducer &&
-                  B200MOE_STIMEOUT_LAST == kStatusTimeoutEpilogue && B200MOE_SWRONGARCH == kStatusWrongArch,
+                  B200MOE_STIMEOUT_LAST == kStatusTimeoutEpilogue && B200MOE_SSELFTEST == kStatusSelfTestTimeout && B200MOE_SWRONGARCH == kStatusWrongArch,
               "public and internal status codes must agree");
 
 extern "C" {
@@ -108,6 +108,10 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
     return grouped_gemm_fp8_block_launch(a);
 }
 
+int b200moe_selftest_wait_timeout(uint64_t limit_ns, int32_t* status, b200moe_stream_t stream) {
+    return selftest_wait_launch(limit_ns, status, static_cast<cudaStream_t>(stream));
+}
+
 int b200moe_route_workspace_bytes(int R, int E, size_t* bytes) {
     if (bytes == nullptr) return kErrBadArgument;
     int chunk_len = 0, num_chunks = 0;
@@ -135,6 +139,27 @@ int b200moe_route_noalloc(const int32_t* ids, int R, int E, int32_t* m_sizes, in
     if (R > 0 && (ids == nullptr || perm == nullptr || inv_perm == nullptr)) return kErrBadArgument;
     return route_static_launch(ids, R, E, m_sizes, offsets, perm, inv_perm, status,
                                static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_moe_align_workspace_bytes(int R, int E, size_t* bytes) {
+    if (bytes == nullptr) return kErrBadArgument;
+    const long long n = align_blocks_scratch_ints(R, E);
+    if (n < 0) return kErrBadArgument;
+    *bytes = sizeof(int32_t) * static_cast<size_t>(n);
+    return 0;
+}
+
+int b200moe_moe_align_block_size(const int32_t* ids, int R, int E, int block_size, int32_t* sorted_ids,
+                                 int32_t* expert_ids, int32_t* num_tokens_post_pad, void* workspace,
+                                 size_t workspace_bytes, int32_t* status, b200moe_stream_t stream) {
+    size_t need = 0;
+    if (int e = b200moe_moe_align_workspace_bytes(R, E, &need)) return e;
+    if (sorted_ids == nullptr || expert_ids == nullptr || num_tokens_post_pad == nullptr || workspace == nullptr ||
+        (R > 0 && ids == nullptr))
+        return kErrBadArgument;
+    if (workspace_bytes < need) return kErrTooLarge;
+    return align_blocks_launch(ids, R, E, block_size, sorted_ids, expert_ids, num_tokens_post_pad,
+                               static_cast<int32_t*>(workspace), status, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_gather_rows(const void* src, const int32_t* idx, int div, void* dst, int rows, int64_t row_bytes,

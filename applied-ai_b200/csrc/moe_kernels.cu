@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "b200moe_internal.h"
@@ -172,6 +173,85 @@ int route_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* of
     route_scatter_kernel<<<blocks, kRouteWarps * 32, sizeof(int32_t) * (kRouteWarps + 1) * E, stream>>>(
         ids, R, E, chunk_len, num_chunks, counts, m_sizes, offsets, perm, inv_perm);
     return static_cast<int>(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------ padded layout (vLLM format)
+// From the routing result, the three arrays moe_align_block_size returns
+// (kernels/triton/inference/col_major_moe_gemm/v0_moe_fused.py:138-180): every expert's rows
+// padded to a multiple of block_size with the pad id `numel`, one expert id per block, and
+// the padded total.  sorted_ids must arrive pre-filled with the pad id.
+__global__ void __launch_bounds__(256)
+align_blocks_kernel(const int32_t* __restrict__ m_sizes, const int32_t* __restrict__ offsets,
+                    const int32_t* __restrict__ perm, int R, int E, int block_size,
+                    int32_t* __restrict__ sorted_ids, int32_t* __restrict__ expert_ids,
+                    int32_t* __restrict__ num_tokens_post_pad) {
+    extern __shared__ int32_t padded_off[];  // [E + 1] exclusive prefix of the padded sizes
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < E; ++e) {
+            padded_off[e] = acc;
+            acc += (m_sizes[e] + block_size - 1) / block_size * block_size;
+        }
+        padded_off[E] = acc;
+        if (blockIdx.x == 0) num_tokens_post_pad[0] = acc;
+    }
+    __syncthreads();
+    const int stride = gridDim.x * blockDim.x;
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+    // one expert id per block of the padded layout
+    const int nblocks = padded_off[E] / block_size;
+    for (int b = tid; b < nblocks; b += stride) {
+        const int pos = b * block_size;
+        int lo = 0, hi = E - 1;  // last e with padded_off[e] <= pos and a non-empty padded range
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (padded_off[mid] <= pos) lo = mid; else hi = mid - 1;
+        }
+        expert_ids[b] = lo;
+    }
+    // routed rows to their padded positions
+    for (int p = tid; p < R; p += stride) {
+        int lo = 0, hi = E - 1;  // expert of sorted position p: last e with offsets[e] <= p
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (offsets[mid] <= p) lo = mid; else hi = mid - 1;
+        }
+        sorted_ids[padded_off[lo] + (p - offsets[lo])] = perm[p];
+    }
+}
+
+__global__ void fill_i32_kernel(int32_t* dst, long long n, int32_t value) {
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        dst[i] = value;
+}
+
+int align_blocks_launch(const int32_t* ids, int R, int E, int block_size, int32_t* sorted_ids, int32_t* expert_ids,
+                        int32_t* num_tokens_post_pad, int32_t* scratch, int32_t* status, cudaStream_t stream) {
+    if (block_size <= 0) return kErrBadArgument;
+    int chunk_len = 0, num_chunks = 0;
+    if (int e = route_plan(R, E, &chunk_len, &num_chunks)) return e;
+    // scratch: m_sizes[E] | offsets[E+1] | perm[R] | inv_perm[R] | counts[num_chunks*E]
+    int32_t* m_sizes = scratch;
+    int32_t* offsets = m_sizes + E;
+    int32_t* perm = offsets + E + 1;
+    int32_t* inv_perm = perm + R;
+    int32_t* counts = inv_perm + R;
+    if (int e = route_launch(ids, R, E, m_sizes, offsets, perm, inv_perm, counts, status, stream)) return e;
+    const long long n_sorted = static_cast<long long>(R) + static_cast<long long>(E) * (block_size - 1);
+    fill_i32_kernel<<<static_cast<int>(std::min<long long>((n_sorted + 255) / 256, 1184)), 256, 0, stream>>>(
+        sorted_ids, n_sorted, R);
+    const int blocks = std::max(1, std::min((R + 255) / 256, 592));
+    align_blocks_kernel<<<blocks, 256, sizeof(int32_t) * (E + 1), stream>>>(m_sizes, offsets, perm, R, E, block_size,
+                                                                             sorted_ids, expert_ids,
+                                                                             num_tokens_post_pad);
+    return static_cast<int>(cudaGetLastError());
+}
+
+long long align_blocks_scratch_ints(int R, int E) {
+    int chunk_len = 0, num_chunks = 0;
+    if (route_plan(R, E, &chunk_len, &num_chunks)) return -1;
+    return static_cast<long long>(E) + (E + 1) + 2ll * R + static_cast<long long>(std::max(num_chunks, 1)) * E;
 }
 
 // ------------------------------------------------------------------ routing, scratch held by the library

@@ -17,6 +17,10 @@ int route_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* of
 int route_static_capacity_ints();
 int route_static_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
                         int32_t* inv_perm, int32_t* status, cudaStream_t stream);
+// vLLM-format padded layout built on the routing kernels; scratch = align_blocks_scratch_ints() int32.
+long long align_blocks_scratch_ints(int R, int E);
+int align_blocks_launch(const int32_t* ids, int R, int E, int block_size, int32_t* sorted_ids, int32_t* expert_ids,
+                        int32_t* num_tokens_post_pad, int32_t* scratch, int32_t* status, cudaStream_t stream);
 int gather_rows_launch(const void* src, const int32_t* idx, int div, void* dst, int rows, long long row_bytes,
                        int src_rows, cudaStream_t stream);
 int swiglu_launch(const void* in, void* out, long long rows, int d, cudaStream_t stream);

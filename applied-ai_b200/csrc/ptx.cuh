@@ -78,14 +78,15 @@ constexpr uint64_t kWaitLimitNs = 400ull * 1000ull * 1000ull;
 
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA:
 // once any role gives up, every other role's next check gives up too.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if (((++spins) & 0x3F) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }

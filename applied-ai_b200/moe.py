@@ -62,6 +62,34 @@ def route(topk_ids, num_experts, *, check=None):
     return m_sizes, offsets, perm, inv_perm
 
 
+def moe_align_block_size(topk_ids, block_size, num_experts):
+    """(sorted_token_ids, expert_ids, num_tokens_post_padded) with the buffer sizes, pad id and
+    ordering of the reference wrapper (v0_moe_fused.py:138-180): each expert's routed rows padded
+    to a multiple of block_size with the id `topk_ids.numel()`.  For code written against the
+    vLLM format; this engine's own GEMM does not need the padding."""
+    _gg._require(topk_ids.is_cuda, "topk_ids must be a CUDA tensor (no CPU path)")
+    ids = topk_ids.reshape(-1)
+    if ids.dtype != torch.int32:
+        ids = ids.to(torch.int32)
+    ids = ids.contiguous()
+    R, E, dev = ids.numel(), int(num_experts), ids.device
+    sorted_ids = torch.empty(R + E * (block_size - 1), dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(R + E, dtype=torch.int32, device=dev)
+    post_pad = torch.empty(1, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    import ctypes
+    need = ctypes.c_size_t(0)
+    _lib.check(lib.b200moe_moe_align_workspace_bytes(R, E, ctypes.byref(need)), "moe_align_block_size")
+    ws = _workspace(dev, need.value)
+    word = _gg._status_word(dev)
+    with torch.cuda.device(dev):
+        rc = lib.b200moe_moe_align_block_size(ids.data_ptr(), R, E, int(block_size), sorted_ids.data_ptr(),
+                                              expert_ids.data_ptr(), post_pad.data_ptr(), ws.data_ptr(), ws.numel(),
+                                              word.data_ptr(), _stream(ids))
+    _lib.check(rc, "moe_align_block_size")
+    return sorted_ids, expert_ids, post_pad
+
+
 def gather_rows(src, idx, div=1, out=None):
     """out[p, :] = src[idx[p] // div, :] (idx int32 on the device)."""
     _gg._require(src.is_cuda and idx.is_cuda and src.is_contiguous() and idx.is_contiguous(),

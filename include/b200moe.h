@@ -38,6 +38,7 @@ typedef void* b200moe_stream_t;
 #define B200MOE_SBADSIZES 1        /* negative m_sizes entry, sum(m_sizes) > M, or an expert id outside [0, E) */
 #define B200MOE_STIMEOUT_FIRST 16  /* 16..19: a bounded wait inside the GEMM kernel ran out */
 #define B200MOE_STIMEOUT_LAST 19
+#define B200MOE_SSELFTEST 20       /* b200moe_selftest_wait_timeout: the unsatisfied wait ran out, as it should */
 #define B200MOE_SWRONGARCH 32
 
 /* flags of the grouped GEMM entry points */
@@ -88,6 +89,13 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
                                        const int32_t* y_row_map, int y_rows, int32_t* status,
                                        b200moe_stream_t stream);
 
+/* Failure-path self-test: launches one small kernel whose only wait can never be
+ * satisfied and whose limit is limit_ns (1 .. 2e9).  After the limit the kernel stops
+ * polling, writes B200MOE_SSELFTEST to *status and returns; nothing faults and the
+ * context stays usable.  Every wait inside the GEMM kernels ends the same way (codes
+ * 16..19, limit 0.4 s).  No counterpart in the reference, which has no bounded waits. */
+int b200moe_selftest_wait_timeout(uint64_t limit_ns, int32_t* status, b200moe_stream_t stream);
+
 /* Routing: stable counting sort of ids[R] (R = tokens*top_k, flat index t*top_k + j)
  * by expert.  m_sizes[E], offsets[E+1], perm[R] (sorted position -> flat index),
  * inv_perm[R] (flat index -> sorted position, -1 for an id outside [0,E)).
@@ -118,6 +126,16 @@ int b200moe_route(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* o
  * each call overwrites every entry it later reads. */
 int b200moe_route_noalloc(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* offsets, int32_t* perm,
                           int32_t* inv_perm, int32_t* status, b200moe_stream_t stream);
+
+/* The padded layout of moe_align_block_size(topk_ids, block_size, num_experts)
+ * (kernels/triton/inference/col_major_moe_gemm/v0_moe_fused.py:138-180), for code written
+ * against that format: sorted_ids[R + E*(block_size-1)] = routed rows grouped by expert,
+ * each expert padded to a multiple of block_size with the pad id R; expert_ids[>= R/block_size + E]
+ * = expert of every block (entries past the used blocks are not written); num_tokens_post_pad[1]. */
+int b200moe_moe_align_workspace_bytes(int R, int E, size_t* bytes);
+int b200moe_moe_align_block_size(const int32_t* ids, int R, int E, int block_size, int32_t* sorted_ids,
+                                 int32_t* expert_ids, int32_t* num_tokens_post_pad, void* workspace,
+                                 size_t workspace_bytes, int32_t* status, b200moe_stream_t stream);
 
 /* dst[p, :] = src[idx[p] / div, :] for p < rows; row_bytes bytes per row.  The
  * indexed load the reference's GEMM does per tile (v0_moe_fused.py:95, offs_token //

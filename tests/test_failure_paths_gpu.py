@@ -1,0 +1,40 @@
+"""Device-side waits are bounded: a wait that nothing satisfies ends with a status code,
+not a hang, and the context keeps working.  No GPU fault, trap or endless loop is used."""
+import time
+
+import pytest
+import torch
+
+import applied_ai_b200 as B
+from applied_ai_b200 import _lib
+from oracle import grouped as O
+
+pytestmark = pytest.mark.gpu
+
+
+def test_unsatisfied_wait_returns_status_and_context_survives():
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0 = time.time()
+    rc = lib.b200moe_selftest_wait_timeout(50_000_000, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    dt = time.time() - t0
+    assert int(status.item()) == 20
+    assert 0.04 <= dt < 2.0, dt            # it waited for its 50 ms limit, then gave up by itself
+    assert "expected" in _lib.describe_status(20)
+    # same context, next launch: a real grouped GEMM still works and is right
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(200, 64, generator=g).to(torch.bfloat16)
+    w = torch.randn(2 * 64, 64, generator=g).to(torch.bfloat16)
+    m = torch.tensor([120, 80], dtype=torch.int32)
+    y = B.grouped_gemm(x.cuda(), w.cuda(), m.cuda())
+    assert O.rel_err(y.cpu().float(), O.grouped_gemm_ref(x, w, m)) <= 1e-2
+
+
+def test_selftest_rejects_unbounded_limits():
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.b200moe_selftest_wait_timeout(0, status.data_ptr(), None) == -1
+    assert lib.b200moe_selftest_wait_timeout(10_000_000_000, status.data_ptr(), None) == -1
+    assert lib.b200moe_selftest_wait_timeout(1000, None, None) == -1

@@ -42,6 +42,27 @@ def test_route_rejects_bad_ids():
         B.route(torch.zeros(4, 2, dtype=torch.int32, device=DEV), 4096)
 
 
+def test_moe_align_block_size_matches_reference_format():
+    """Docstring example of the reference (v0_moe_fused.py:157-165) and random cases vs the oracle."""
+    import json
+    import os
+    from tests.helpers import GOLDEN
+    ex = json.load(open(os.path.join(GOLDEN, "align_example.json")))
+    ids = torch.tensor(ex["topk_ids"], dtype=torch.int32)
+    s, e, p = B.moe_align_block_size(ids.to(DEV), ex["block_size"], 5)
+    assert s.numel() == ids.numel() + 5 * (ex["block_size"] - 1) and e.numel() == ids.numel() + 5
+    assert s[: int(p)].tolist() == ex["sorted_token_ids"] and int(p) == 16
+    assert e[: int(p) // ex["block_size"]].tolist() == [1, 2, 3, 4]
+    g = torch.Generator().manual_seed(8)
+    for (T, k, E, blk) in [(64, 2, 8, 16), (1000, 8, 256, 64), (4096, 2, 8, 64), (5, 1, 3, 128)]:
+        ids = torch.randint(0, E, (T, k), generator=g, dtype=torch.int32)
+        s, e, p = B.moe_align_block_size(ids.to(DEV), blk, E)
+        rs, re_, rp = O.moe_align_block_size_ref(ids, blk, E)
+        assert torch.equal(p.cpu(), rp) and torch.equal(s.cpu(), rs)
+        nb = int(rp) // blk
+        assert torch.equal(e.cpu()[:nb], re_[:nb])
+
+
 def test_gather_rows():
     g = torch.Generator().manual_seed(2)
     for (T, H, k, dtype) in [(64, 4096, 2, torch.bfloat16), (33, 7168, 8, torch.bfloat16), (50, 56, 2, torch.float32),
