@@ -34,6 +34,9 @@ struct GGParams {
     const float* w_scale;
     int32_t* status;
     const int32_t* row_map;        // optional: row r of the result is stored at row row_map[r] of y
+    const float* c_in;             // fp32 epilogue: the C operand of alpha*acc + beta*C (same layout as y)
+    float alpha, beta;
+    uint32_t idesc;                // tcgen05 instruction descriptor (operand formats, tile shape)
     int y_rows;                    // rows of y (bounds for row_map)
     long long ldy;                 // elements between consecutive rows of y
     long long y_col_group_stride;  // first column of group g's block is g * this (0: all groups share columns)
@@ -51,13 +54,16 @@ struct GGLaunch {
     const float* w_scale;
     int32_t* status;
     const int32_t* row_map;
+    const float* c_in;
+    float alpha, beta;
+    int is_f16;      // 2-byte operands are IEEE half instead of bf16
     int y_rows;
     long long ldy;
     long long y_col_group_stride;
     int M, N, K, G;
-    int elem_bytes;  // 2 bf16, 1 e4m3
+    int elem_bytes;  // 2 bf16/f16, 1 e4m3
     int scale_mode;  // 0 none, 1 row-wise
-    int epilogue;    // 0 plain, 1 SwiGLU
+    int epilogue;    // 0 plain, 1 SwiGLU, 2 fp32 out = alpha*acc + beta*C
     int cta_group;   // 0 auto, 1 or 2
     cudaStream_t stream;
 };

@@ -108,6 +108,31 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
     return grouped_gemm_fp8_block_launch(a);
 }
 
+int b200moe_sm100_gemm_f16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, float alpha,
+                           float beta, b200moe_stream_t stream) {
+    GGLaunch a{};
+    a.x = A;
+    a.w = B;
+    a.m_sizes = nullptr;  // one group: every row
+    a.y = D;
+    a.c_in = static_cast<const float*>(C);
+    a.alpha = alpha;
+    a.beta = beta;
+    a.is_f16 = 1;
+    a.ldy = N;
+    a.y_col_group_stride = 0;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.G = 1;
+    a.elem_bytes = 2;
+    a.scale_mode = 0;
+    a.epilogue = 2;
+    a.cta_group = 0;
+    a.stream = static_cast<cudaStream_t>(stream);
+    return grouped_gemm_launch(a);
+}
+
 int b200moe_selftest_wait_timeout(uint64_t limit_ns, int32_t* status, b200moe_stream_t stream) {
     return selftest_wait_launch(limit_ns, status, static_cast<cudaStream_t>(stream));
 }

@@ -122,7 +122,8 @@ __device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GG
     int row_carry = 0, tile_carry = 0, bad = 0;
     for (int base = 0; base < p.G; base += 32) {
         const int g = base + lane;
-        int m = g < p.G ? p.m_sizes[g] : 0;
+        // no size array = one group holding every row (the dense case)
+        int m = g < p.G ? (p.m_sizes != nullptr ? p.m_sizes[g] : p.M) : 0;
         if (m < 0) {
             bad = 1;
             m = 0;
@@ -234,14 +235,15 @@ inline EncodeTiledFn get_encode_fn() {
 }
 
 // x viewed as [rows, K]; box = 128 rows x 128 bytes, 128-byte swizzle.
-inline int encode_x_map(CUtensorMap* m, const void* x, int rows, int K, int elem_bytes) {
+inline int encode_x_map(CUtensorMap* m, const void* x, int rows, int K, int elem_bytes, bool is_f16 = false) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return kErrNoDriverEntry;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * elem_bytes};
     cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), 128};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+    CUresult r = enc(m, elem_bytes == 2 ? (is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)
+                                     : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                      const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -251,7 +253,8 @@ inline int encode_x_map(CUtensorMap* m, const void* x, int rows, int K, int elem
 // w viewed as [G, rows_per_group, K]; box = 1 group x 128 rows x 128 bytes.  The group
 // is its own dimension so a box that runs past a group's last row is zero-filled
 // instead of reading the next expert's weights.
-inline int encode_w_map(CUtensorMap* m, const void* w, int G, int rows_per_group, int K, int elem_bytes) {
+inline int encode_w_map(CUtensorMap* m, const void* w, int G, int rows_per_group, int K, int elem_bytes,
+                        bool is_f16 = false) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return kErrNoDriverEntry;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows_per_group),
@@ -260,7 +263,8 @@ inline int encode_w_map(CUtensorMap* m, const void* w, int G, int rows_per_group
                              static_cast<cuuint64_t>(K) * elem_bytes * rows_per_group};
     cuuint32_t box[3] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), 128, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+    CUresult r = enc(m, elem_bytes == 2 ? (is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)
+                                     : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
                      const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -31,7 +31,9 @@ constexpr int kEpiWarps = 4;
 
 // ELEM_BYTES: 2 = bf16 operands, 1 = e4m3 operands.
 // SCALE: 0 none, 1 row-wise (x_scale[M], w_scale[G*N]).
-// EPI: 0 plain, 1 SwiGLU (w[g] = [gate rows 0..I) ; up rows I..2I), output has I columns).
+// EPI: 0 plain, 1 SwiGLU (w[g] = [gate rows 0..I) ; up rows I..2I), output has I columns),
+//      2 fp32 output alpha*acc + beta*C (the dense D = alpha*A*B^T + beta*C of
+//        kernels/blackwell/cute_gemm_02_tma/sm100_gemm.cu:157-173).
 template <int ELEM_BYTES, int CTAS, int SCALE, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GGParams p) {
@@ -40,7 +42,6 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
     constexpr bool kFp8 = ELEM_BYTES == 1;
     constexpr int kElemsPerStage = kRowBytes / ELEM_BYTES;  // K elements per stage
     constexpr int kTileRows = kRowsPerCta * CTAS;
-    constexpr uint32_t kIdesc = make_idesc(kFp8, kTileRows, kTileN);
 
     extern __shared__ uint8_t smem_raw[];
     const SmemView sv = carve_smem<CTAS>(smem_raw);
@@ -111,7 +112,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         // 32 bytes along K per MMA: +2 in the descriptor's 16-byte units.
-                        umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc,
+                        umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
                                          (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit<CTAS>(&st->empty[stage]);
@@ -191,7 +192,33 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                         f[j] = f[j] * x_scale * ws;
                     }
                 }
-                if (store_ok) {
+                if constexpr (EPI == 2) {
+                    if (store_ok) {
+                        const size_t off = static_cast<size_t>(drow) * p.ldy + col;
+                        float* d32 = static_cast<float*>(p.y) + off;
+                        const float* c32 = p.c_in + off;
+                        const bool use_c = p.beta != 0.0f;
+                        if ((col + 32 <= p.n_out) && ((reinterpret_cast<uintptr_t>(d32) & 15u) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(c32) & 15u) == 0)) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                float4 cv = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (use_c) cv = __ldg(reinterpret_cast<const float4*>(c32) + q);
+                                float4 o;
+                                o.x = p.alpha * f[q * 4 + 0] + p.beta * cv.x;
+                                o.y = p.alpha * f[q * 4 + 1] + p.beta * cv.y;
+                                o.z = p.alpha * f[q * 4 + 2] + p.beta * cv.z;
+                                o.w = p.alpha * f[q * 4 + 3] + p.beta * cv.w;
+                                reinterpret_cast<float4*>(d32)[q] = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < p.n_out)
+                                    d32[j] = p.alpha * f[j] + (use_c ? p.beta * c32[j] : 0.0f);
+                        }
+                    }
+                } else if (store_ok) {
                     __nv_bfloat16* dst = y_row + col;
                     const bool vec = (col + 32 <= p.n_out) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
                     if (vec) {
@@ -272,16 +299,19 @@ static int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, cons
 
 int grouped_gemm_launch(const GGLaunch& a) {
     if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0 || a.x == nullptr || a.w == nullptr || a.y == nullptr ||
-        a.m_sizes == nullptr)
+        (a.m_sizes == nullptr && a.G != 1))
         return kErrBadArgument;
     if (a.G > kMaxGroups) return kErrTooManyGroups;
     if (a.elem_bytes != 1 && a.elem_bytes != 2) return kErrBadArgument;
     if ((static_cast<long long>(a.K) * a.elem_bytes) % 16 != 0) return kErrAlignment;  // TMA row pitch
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.w) & 15u)) return kErrAlignment;
     if (a.scale_mode == 1 && (a.x_scale == nullptr || a.w_scale == nullptr)) return kErrBadArgument;
+    if (a.epilogue == 2 && (a.elem_bytes != 2 || a.scale_mode != 0 || a.y_col_group_stride != 0 ||
+                            (a.beta != 0.0f && a.c_in == nullptr) || a.row_map != nullptr))
+        return kErrBadArgument;
     if (a.scale_mode != 0 && a.scale_mode != 1) return kErrBadArgument;
     if (a.epilogue == 1 && (a.N % 2 != 0)) return kErrBadArgument;
-    if (a.epilogue != 0 && a.epilogue != 1) return kErrBadArgument;
+    if (a.epilogue < 0 || a.epilogue > 2) return kErrBadArgument;
     if (a.epilogue == 1 && a.scale_mode != 0) return kErrBadArgument;
     if (a.M == 0) return 0;
 
@@ -290,8 +320,8 @@ int grouped_gemm_launch(const GGLaunch& a) {
     if (di.cc_major != 10) return kErrWrongDevice;
 
     CUtensorMap tm_x, tm_w;
-    if (int e = encode_x_map(&tm_x, a.x, a.M, a.K, a.elem_bytes)) return e;
-    if (int e = encode_w_map(&tm_w, a.w, a.G, a.N, a.K, a.elem_bytes)) return e;
+    if (int e = encode_x_map(&tm_x, a.x, a.M, a.K, a.elem_bytes, a.is_f16 != 0)) return e;
+    if (int e = encode_w_map(&tm_w, a.w, a.G, a.N, a.K, a.elem_bytes, a.is_f16 != 0)) return e;
 
     GGParams p;
     p.m_sizes = a.m_sizes;
@@ -314,11 +344,16 @@ int grouped_gemm_launch(const GGLaunch& a) {
     // would be padding, so small groups use the single-CTA 128-row tile.
     const int ctas = a.cta_group == 1 ? 1 : a.cta_group == 2 ? 2 : (a.M / a.G >= 256 ? 2 : 1);
     const bool fp8 = a.elem_bytes == 1;
+    p.c_in = a.c_in;
+    p.alpha = a.alpha;
+    p.beta = a.beta;
+    p.idesc = make_idesc(fp8, 128 * ctas, kTileN, a.is_f16 != 0);
 #define B200MOE_LAUNCH(EB, SC, EP)                                                          \
     (ctas == 1 ? launch_variant<EB, 1, SC, EP>(tm_x, tm_w, p, di.sms, a.stream)              \
                : launch_variant<EB, 2, SC, EP>(tm_x, tm_w, p, di.sms, a.stream))
     if (!fp8 && a.epilogue == 0) return B200MOE_LAUNCH(2, 0, 0);
     if (!fp8 && a.epilogue == 1) return B200MOE_LAUNCH(2, 0, 1);
+    if (!fp8 && a.epilogue == 2) return B200MOE_LAUNCH(2, 0, 2);
     if (fp8 && a.scale_mode == 1) return B200MOE_LAUNCH(1, 1, 0);
     if (fp8 && a.scale_mode == 0 && a.epilogue == 0) return B200MOE_LAUNCH(1, 0, 0);
 #undef B200MOE_LAUNCH

@@ -33,7 +33,6 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
     using Cfg = StageCfg<CTAS>;
     constexpr int kTileRows = kRowsPerCta * CTAS;
-    constexpr uint32_t kIdesc = make_idesc(true, kTileRows, kTileN);
 
     extern __shared__ uint8_t smem_raw[];
     const SmemView sv = carve_smem<CTAS>(smem_raw);
@@ -103,7 +102,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     const uint64_t b_desc = make_sw128_kmajor_desc(a_addr + kABytes);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma<CTAS, true>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, k > 0 ? 1u : 0u);
+                        umma<CTAS, true>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
                     umma_commit<CTAS>(&st->empty[stage]);
                     umma_commit<CTAS>(&st->acc_full[buf]);
                     if (++stage == Cfg::kStages) {
@@ -306,6 +305,10 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.n_tiles = a.epilogue == 1 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;
 
     const int ctas = a.cta_group == 1 ? 1 : a.cta_group == 2 ? 2 : (a.M / a.G >= 256 ? 2 : 1);
+    p.c_in = nullptr;
+    p.alpha = 1.0f;
+    p.beta = 0.0f;
+    p.idesc = make_idesc(true, 128 * ctas, kTileN);
     if (a.epilogue == 0)
         return ctas == 1 ? launch_block_variant<1, 0>(tm_x, tm_w, p, di.sms, a.stream)
                          : launch_block_variant<2, 0>(tm_x, tm_w, p, di.sms, a.stream);

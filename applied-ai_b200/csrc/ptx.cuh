@@ -192,8 +192,8 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
 // fp32 accumulate, both operands K-major.
 // Bits: [4,6) D format (1 = f32), [7,10) A format, [10,13) B format,
 // [15] A major, [16] B major (0 = K), [17,23) N>>3, [24,29) M>>4.
-__host__ __device__ constexpr uint32_t make_idesc(bool is_fp8, int mma_m, int mma_n) {
-    const uint32_t fmt = is_fp8 ? 0u /* E4M3 */ : 1u /* BF16 */;
+__host__ __device__ constexpr uint32_t make_idesc(bool is_fp8, int mma_m, int mma_n, bool is_f16 = false) {
+    const uint32_t fmt = is_fp8 ? 0u /* E4M3 */ : (is_f16 ? 0u /* F16 */ : 1u /* BF16 */);
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(mma_n >> 3) << 17) |
            (static_cast<uint32_t>(mma_m >> 4) << 24);
 }

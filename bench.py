@@ -615,13 +615,78 @@ def run_layer(args):
         dist.destroy_process_group()
 
 
+def run_dense(args):
+    """Dense fp16 GEMM D = A @ B^T (fp32 out) at one expert's worth of the C2 shape: this
+    package's single-group mode next to the reference's own Blackwell kernel
+    (launch_sm100_gemm_f16_tma, built by oracle/build_ref.py into oracle/_ref/)."""
+    import ctypes
+    from applied_ai_b200 import _lib, sm100_gemm as S
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    _lib.load(build_if_missing=False)
+    dev = torch.device("cuda", 0)
+    M, N, K = 16384, 4096, 7168
+    g = torch.Generator(device=dev).manual_seed(77)
+    A = torch.randn(M, K, generator=g, device=dev).to(torch.float16)
+    Bm = (torch.randn(N, K, generator=g, device=dev) * K ** -0.5).to(torch.float16)
+    C = torch.zeros(M, N, dtype=torch.float32, device=dev)
+    flops = 2.0 * M * N * K
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    D = S.sm100_gemm_f16(A, Bm, C)
+    from oracle import grouped as O
+    pick = torch.tensor([0, M // 3, M - 1], device=dev)
+    err = O.rel_err(D[pick].cpu(), A[pick].cpu().float() @ Bm.cpu().float().T)
+    assert err <= 1e-3, err
+    ms_ours = timed(lambda: S.sm100_gemm_f16(A, Bm, C))
+    ref_info = {"unavailable": "oracle/_ref/libsm100_gemm_ref.so not built"}
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libsm100_gemm_ref.so")
+    if os.path.exists(ref_path):
+        ref = ctypes.CDLL(ref_path)
+        fn = ref.launch_sm100_gemm_f16_tma
+        fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 3 + [ctypes.c_float] * 2 + [ctypes.c_void_p]
+        fn.restype = ctypes.c_int
+        D2 = torch.empty_like(C)
+        rc = fn(A.data_ptr(), Bm.data_ptr(), C.data_ptr(), D2.data_ptr(), M, N, K, 1.0, 0.0, None)
+        torch.cuda.synchronize()
+        if rc == 0:
+            ms_ref = timed(lambda: fn(A.data_ptr(), Bm.data_ptr(), C.data_ptr(), D2.data_ptr(), M, N, K, 1.0, 0.0, None))
+            ref_info = {"ms_per_step": ms_ref, "tflops": flops / (ms_ref * 1e-3) / 1e12,
+                        "max_rel_diff_vs_ours": O.rel_err(D2[pick].cpu(), D[pick].cpu()),
+                        "what": "kernels/blackwell/cute_gemm_02_tma/sm100_gemm.cu built unmodified"}
+        else:
+            ref_info = {"unavailable": f"reference launcher returned {rc}"}
+    peaks = load_peaks()
+    tf = flops / (ms_ours * 1e-3) / 1e12
+    line = {"metric": "dense_gemm_tflops", "value": tf, "unit": "TFLOPS", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_ours, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"dense: D = A @ B^T, fp16 in, fp32 out, M={M} N={N} K={K}",
+                       "l2": "operands 561 MiB > 126 MiB L2"},
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": tf / peaks["bf16_tflops"], "traffic": args.traffic,
+                         "peak_source": peaks["source"] + " (burst cuBLAS bf16)"},
+            "reference_kernel": ref_info, "gpu_launches": args.steps}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(LAYERS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(LAYERS) + ["dense"])
     ap.add_argument("--cta-group", type=int, default=0, dest="cta_group")
     ap.add_argument("--waves", type=int, default=2,
                     help="expert-parallel layers: chunks of local experts whose exchange overlaps compute")
@@ -630,6 +695,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "dense":
+        run_dense(args)
     elif args.workload in LAYERS:
         run_layer(args)
     else:

@@ -89,6 +89,16 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
                                        const int32_t* y_row_map, int y_rows, int32_t* status,
                                        b200moe_stream_t stream);
 
+/* Dense D = alpha * A @ B^T + beta * C with the grouped kernel's G = 1 mode.
+ * A [M,K], B [N,K] IEEE half (float16), C and D [M,N] float32, row-major; C may be NULL
+ * when beta == 0.  Same arguments as
+ *   launch_sm100_gemm_f16_tma(void* A, void* B, void* C, void* D, int M, int N, int K,
+ *                             float alpha, float beta, cudaStream_t)
+ * kernels/blackwell/cute_gemm_02_tma/sm100_gemm.h:33-36, without its alignment rules
+ * (M % 128, N % 256, K % 64): any M, N and K % 8 == 0 work, and the stream argument is honoured. */
+int b200moe_sm100_gemm_f16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, float alpha,
+                           float beta, b200moe_stream_t stream);
+
 /* Failure-path self-test: launches one small kernel whose only wait can never be
  * satisfied and whose limit is limit_ns (1 .. 2e9).  After the limit the kernel stops
  * polling, writes B200MOE_SSELFTEST to *status and returns; nothing faults and the

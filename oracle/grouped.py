@@ -156,6 +156,12 @@ def quant_1x128_ref(x, block=128):
     return q.reshape(x.shape), scale
 
 
+def dense_gemm_ref(A, B, C, alpha=1.0, beta=0.0):
+    """alpha * A @ B.T + beta * C in fp32 — what the reference's Blackwell driver compares
+    against with torch.addmm (kernels/blackwell/cute_gemm_02_tma/driver.py:240-258)."""
+    return alpha * (A.float() @ B.float().T) + beta * C.float()
+
+
 def rel_err(y, ref):
     """max|y - ref| / max|ref|, the normalisation printed by
     kernels/blackwell/cute_gemm_02_tma/driver.py:257-258."""
