@@ -31,6 +31,7 @@ STATUS_NAMES = {
     18: "device-side wait ran out (MMA issuer, accumulator)",
     19: "device-side wait ran out (epilogue)",
     20: "self-test wait ran out (expected)",
+    24: "expert-parallel dispatch: a rank would receive more rows than its receive buffer holds",
     32: "kernel image not built for sm_100a",
 }
 
@@ -44,6 +45,14 @@ SIGNATURES = {
                                          _c_i64, _c_i64, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
     "b200moe_grouped_gemm_fp8_blockwise": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
                                            _c_i64, _c_i64, _c_int, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
+    "b200moe_grouped_gemm_ex": [_c_vp, _c_vp],
+    "b200moe_ep_plan": [_c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp],
+    "b200moe_ep_push": [_c_vp, _c_i64, _c_vp, _c_i64, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
+                        _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp],
+    "b200moe_enable_peer_access": [_c_int],
+    "b200moe_ipc_open": [_c_vp, ctypes.POINTER(_c_vp)],
+    "b200moe_ipc_close": [_c_vp],
+    "b200moe_peer_probe": [_c_vp, _c_vp],
     "b200moe_sm100_gemm_f16": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, ctypes.c_float, ctypes.c_float,
                                _c_vp],
     "b200moe_selftest_wait_timeout": [ctypes.c_uint64, _c_vp, _c_vp],
@@ -60,6 +69,15 @@ SIGNATURES = {
 
 _lock = threading.Lock()
 _lib = None
+
+
+class GemmDesc(ctypes.Structure):
+    """Mirror of b200moe_gemm_desc (include/b200moe.h)."""
+    _fields_ = [("x", _c_vp), ("w", _c_vp), ("m_sizes", _c_vp), ("y", _c_vp), ("x_scale", _c_vp), ("w_scale", _c_vp),
+                ("M", _c_int), ("N", _c_int), ("K", _c_int), ("G", _c_int), ("ldy", _c_i64),
+                ("y_col_group_stride", _c_i64), ("kind", _c_int), ("epilogue", _c_int), ("cta_group", _c_int),
+                ("y_rows", _c_int), ("y_row_map", _c_vp), ("y_row_tags", _c_vp), ("y_peer_bases", _c_vp),
+                ("n_peers", _c_int), ("status", _c_vp)]
 
 
 class B200MoeError(RuntimeError):

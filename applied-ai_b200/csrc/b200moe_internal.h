@@ -13,6 +13,7 @@ enum : int32_t {
     kStatusTimeoutMmaAcc = 18,    // MMA issuer gave up waiting for a drained accumulator
     kStatusTimeoutEpilogue = 19,  // epilogue gave up waiting for a finished accumulator
     kStatusSelfTestTimeout = 20,  // the self-test's deliberately unsatisfied wait ran out (expected)
+    kStatusCapacity = 24,         // expert-parallel dispatch: a rank would receive more rows than its buffer holds
     kStatusWrongArch = 32,        // kernel image was not built for sm_100a
 };
 
@@ -34,6 +35,9 @@ struct GGParams {
     const float* w_scale;
     int32_t* status;
     const int32_t* row_map;        // optional: row r of the result is stored at row row_map[r] of y
+    const long long* row_tags;     // optional: row r goes to peer_y[tag >> 32] at row (tag & 0xffffffff)
+    void* const* peer_y;           //   bases of y on every rank (device array, n_peers entries)
+    int n_peers;
     const float* c_in;             // fp32 epilogue: the C operand of alpha*acc + beta*C (same layout as y)
     float alpha, beta;
     uint32_t idesc;                // tcgen05 instruction descriptor (operand formats, tile shape)
@@ -54,6 +58,9 @@ struct GGLaunch {
     const float* w_scale;
     int32_t* status;
     const int32_t* row_map;
+    const long long* row_tags;
+    void* const* peer_y;
+    int n_peers;
     const float* c_in;
     float alpha, beta;
     int is_f16;      // 2-byte operands are IEEE half instead of bf16

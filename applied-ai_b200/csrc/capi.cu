@@ -16,7 +16,7 @@ static_assert(B200MOE_EBADARG == kErrBadArgument && B200MOE_EALIGN == kErrAlignm
                   B200MOE_ETOOLARGE == kErrTooLarge,
               "public and internal error codes must agree");
 static_assert(B200MOE_SBADSIZES == kStatusBadGroupSizes && B200MOE_STIMEOUT_FIRST == kStatusTimeoutProducer &&
-                  B200MOE_STIMEOUT_LAST == kStatusTimeoutEpilogue && B200MOE_SSELFTEST == kStatusSelfTestTimeout && B200MOE_SWRONGARCH == kStatusWrongArch,
+                  B200MOE_STIMEOUT_LAST == kStatusTimeoutEpilogue && B200MOE_SSELFTEST == kStatusSelfTestTimeout && B200MOE_SCAPACITY == kStatusCapacity && B200MOE_SWRONGARCH == kStatusWrongArch,
               "public and internal status codes must agree");
 
 extern "C" {
@@ -107,6 +107,71 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
     if (ldy <= 0 || y_col_group_stride < 0 || (y_row_map != nullptr && y_rows <= 0)) return kErrBadArgument;
     return grouped_gemm_fp8_block_launch(a);
 }
+
+int b200moe_grouped_gemm_ex(const b200moe_gemm_desc* d, b200moe_stream_t stream) {
+    if (d == nullptr) return kErrBadArgument;
+    GGLaunch a{};
+    a.x = d->x;
+    a.w = d->w;
+    a.m_sizes = d->m_sizes;
+    a.y = d->y;
+    a.x_scale = d->x_scale;
+    a.w_scale = d->w_scale;
+    a.status = d->status;
+    a.row_map = d->y_row_map;
+    a.row_tags = reinterpret_cast<const long long*>(d->y_row_tags);
+    a.peer_y = d->y_peer_bases;
+    a.n_peers = d->n_peers;
+    a.y_rows = d->y_rows;
+    a.ldy = d->ldy;
+    a.y_col_group_stride = d->y_col_group_stride;
+    a.M = d->M;
+    a.N = d->N;
+    a.K = d->K;
+    a.G = d->G;
+    a.epilogue = d->epilogue;
+    a.cta_group = d->cta_group;
+    a.stream = static_cast<cudaStream_t>(stream);
+    if (d->ldy <= 0 || d->y_col_group_stride < 0 || d->m_sizes == nullptr) return kErrBadArgument;
+    if ((d->y_row_map != nullptr || d->y_row_tags != nullptr) && d->y_rows <= 0) return kErrBadArgument;
+    if (d->epilogue != B200MOE_EPI_NONE && d->epilogue != B200MOE_EPI_SWIGLU) return kErrBadArgument;
+    switch (d->kind) {
+        case B200MOE_KIND_BF16:
+            a.elem_bytes = 2;
+            a.scale_mode = 0;
+            return grouped_gemm_launch(a);
+        case B200MOE_KIND_FP8_ROWWISE:
+            a.elem_bytes = 1;
+            a.scale_mode = 1;
+            return grouped_gemm_launch(a);
+        case B200MOE_KIND_FP8_BLOCKWISE:
+            a.elem_bytes = 1;
+            a.scale_mode = 2;
+            return grouped_gemm_fp8_block_launch(a);
+        default:
+            return kErrBadArgument;
+    }
+}
+
+int b200moe_ep_plan(const int32_t* counts, int P, int E, int my_rank, int capacity_rows, int32_t* dst_base,
+                    int32_t* m_local, int32_t* status, b200moe_stream_t stream) {
+    return ep_plan_launch(counts, P, E, my_rank, capacity_rows, dst_base, m_local, status,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_push(const void* part0, int64_t row_bytes0, const void* part1, int64_t row_bytes1,
+                    const int32_t* perm, int top_k, const int32_t* offsets, const int32_t* dst_base, int R, int E,
+                    int P, int my_rank, int capacity_rows, int tokens, void* const* peer_part0,
+                    void* const* peer_part1, int64_t* const* peer_tags, b200moe_stream_t stream) {
+    return ep_push_launch(part0, row_bytes0, part1, row_bytes1, perm, top_k, offsets, dst_base, R, E, P, my_rank,
+                          capacity_rows, tokens, peer_part0, peer_part1,
+                          reinterpret_cast<long long* const*>(peer_tags), static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_enable_peer_access(int peer_device) { return enable_peer_access(peer_device); }
+int b200moe_ipc_open(const void* handle64, void** base) { return ipc_open(handle64, base); }
+int b200moe_ipc_close(void* base) { return ipc_close(base); }
+int b200moe_peer_probe(void* peer_ptr, void* local_scratch8) { return peer_probe(peer_ptr, local_scratch8); }
 
 int b200moe_sm100_gemm_f16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, float alpha,
                            float beta, b200moe_stream_t stream) {

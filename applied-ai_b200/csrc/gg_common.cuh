@@ -90,6 +90,33 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 __device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
 
+// Where result row `row` is stored: y itself, y through the caller's row map, or another
+// rank's y through a (rank, row) tag.  Returns false when the row must not be stored.
+struct RowDest {
+    __nv_bfloat16* base;  // start of the destination row's buffer (before the column offset)
+    long long drow;
+};
+__device__ __forceinline__ bool resolve_row_dest(const GGParams& p, int row, bool row_ok, RowDest* out) {
+    out->base = static_cast<__nv_bfloat16*>(p.y);
+    out->drow = row;
+    if (!row_ok) return false;
+    if (p.row_tags != nullptr) {
+        const long long tag = p.row_tags[row];
+        const int rank = static_cast<int>(tag >> 32);
+        const long long pos = tag & 0xffffffffll;
+        if (rank < 0 || rank >= p.n_peers || pos >= p.y_rows) return false;
+        out->base = static_cast<__nv_bfloat16*>(p.peer_y[rank]);
+        out->drow = pos;
+        return true;
+    }
+    if (p.row_map != nullptr) {
+        const int d = __ldg(p.row_map + row);
+        if (d < 0 || d >= p.y_rows) return false;
+        out->drow = d;
+    }
+    return true;
+}
+
 // Stores 32 consecutive fp32 values of one output row as bf16 at columns [col, col+32),
 // clipped to n_out columns; 16-byte stores when the run is whole and aligned.
 __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* y_row, int col, int n_out, const float* f) {

@@ -133,7 +133,6 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t acc_empty_leader =
             CTAS == 1 ? smem_u32(&st->acc_empty[0]) : mapa_shared(smem_u32(&st->acc_empty[0]), 0);
-        __nv_bfloat16* const y = static_cast<__nv_bfloat16*>(p.y);
         int g = 0, buf = 0;
         uint32_t acc_phase = 0;
         for (int t = cluster_id; t < total_tiles; t += num_clusters) {
@@ -154,15 +153,13 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 
             constexpr int kOutCols = EPI == 1 ? 128 : kTileN;  // output columns per tile
             const int col0 = tc.n_idx * kOutCols;              // first output column of the tile (within group)
-            // Destination row: the row itself, or where the caller's row map sends it.
-            int drow = row;
-            bool store_ok = row_ok;
-            if (row_ok && p.row_map != nullptr) {
-                drow = __ldg(p.row_map + row);
-                store_ok = drow >= 0 && drow < p.y_rows;
-            }
-            __nv_bfloat16* const y_row = y + static_cast<size_t>(store_ok ? drow : 0) * p.ldy +
-                                         static_cast<size_t>(tc.g) * p.y_col_group_stride;
+            // Destination row: the row itself, where the caller's row map sends it, or a row of
+            // another rank's buffer.
+            RowDest rd;
+            const bool store_ok = resolve_row_dest(p, row, row_ok, &rd);
+            const long long drow = rd.drow;
+            __nv_bfloat16* const y_row =
+                rd.base + static_cast<size_t>(drow) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
             const float* const w_scale_g = SCALE == 1 ? p.w_scale + static_cast<size_t>(tc.g) * p.N : nullptr;
 
 #pragma unroll 1
@@ -307,11 +304,12 @@ int grouped_gemm_launch(const GGLaunch& a) {
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.w) & 15u)) return kErrAlignment;
     if (a.scale_mode == 1 && (a.x_scale == nullptr || a.w_scale == nullptr)) return kErrBadArgument;
     if (a.epilogue == 2 && (a.elem_bytes != 2 || a.scale_mode != 0 || a.y_col_group_stride != 0 ||
-                            (a.beta != 0.0f && a.c_in == nullptr) || a.row_map != nullptr))
+                            (a.beta != 0.0f && a.c_in == nullptr) || a.row_map != nullptr || a.row_tags != nullptr))
         return kErrBadArgument;
     if (a.scale_mode != 0 && a.scale_mode != 1) return kErrBadArgument;
     if (a.epilogue == 1 && (a.N % 2 != 0)) return kErrBadArgument;
     if (a.epilogue < 0 || a.epilogue > 2) return kErrBadArgument;
+    if (a.row_tags != nullptr && (a.peer_y == nullptr || a.n_peers <= 0 || a.y_rows <= 0)) return kErrBadArgument;
     if (a.epilogue == 1 && a.scale_mode != 0) return kErrBadArgument;
     if (a.M == 0) return 0;
 
@@ -330,7 +328,10 @@ int grouped_gemm_launch(const GGLaunch& a) {
     p.w_scale = a.w_scale;
     p.status = a.status;
     p.row_map = a.row_map;
-    p.y_rows = a.row_map ? a.y_rows : a.M;
+    p.row_tags = a.row_tags;
+    p.peer_y = a.peer_y;
+    p.n_peers = a.n_peers;
+    p.y_rows = (a.row_map || a.row_tags) ? a.y_rows : a.M;
     p.M = a.M;
     p.N = a.N;
     p.K = a.K;

@@ -124,7 +124,6 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t acc_empty_leader =
             CTAS == 1 ? smem_u32(&st->acc_empty[0]) : mapa_shared(smem_u32(&st->acc_empty[0]), 0);
-        __nv_bfloat16* const y = static_cast<__nv_bfloat16*>(p.y);
         const int kblocks = num_kb;                    // scales per row of x
         const int nblocks = (p.N + 127) / 128;         // scale blocks per expert along N
         int g = 0, buf = 0;
@@ -198,15 +197,11 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             if (!ok) break;
 
             // ---- store: the thread's row, its (up to) 128 output columns
-            int drow = row;
-            bool store_ok = row_ok;
-            if (row_ok && p.row_map != nullptr) {
-                drow = __ldg(p.row_map + row);
-                store_ok = drow >= 0 && drow < p.y_rows;
-            }
+            RowDest rd;
+            const bool store_ok = resolve_row_dest(p, row, row_ok, &rd);
             if (store_ok) {
                 __nv_bfloat16* const y_row =
-                    y + static_cast<size_t>(drow) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
+                    rd.base + static_cast<size_t>(rd.drow) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
                 if constexpr (EPI == 1) {
                     const int col = tc.n_idx * 128 + half * 64;  // 64 output columns: silu(gate) * up
 #pragma unroll
@@ -277,6 +272,7 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     if (a.K % 128 != 0) return kErrAlignment;  // whole scale blocks along K
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.w) & 15u)) return kErrAlignment;
     if (a.epilogue != 0 && a.epilogue != 1) return kErrBadArgument;
+    if (a.row_tags != nullptr && (a.peer_y == nullptr || a.n_peers <= 0 || a.y_rows <= 0)) return kErrBadArgument;
     if (a.epilogue == 1 && (a.N % 256 != 0)) return kErrBadArgument;  // gate and up halves in whole scale blocks
     if (a.M == 0) return 0;
 
@@ -294,7 +290,10 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.w_scale = a.w_scale;
     p.status = a.status;
     p.row_map = a.row_map;
-    p.y_rows = a.row_map ? a.y_rows : a.M;
+    p.row_tags = a.row_tags;
+    p.peer_y = a.peer_y;
+    p.n_peers = a.n_peers;
+    p.y_rows = (a.row_map || a.row_tags) ? a.y_rows : a.M;
     p.M = a.M;
     p.N = a.N;
     p.K = a.K;

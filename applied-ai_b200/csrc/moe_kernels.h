@@ -29,4 +29,16 @@ int combine_topk_launch(const void* y, const int32_t* inv_perm, const float* wei
 int quant_1x128_launch(const void* x, int x_is_fp32, void* q, float* scales, long long rows, int K,
                        cudaStream_t stream);
 
+// Expert-parallel dispatch over peer memory (ep_kernels.cu).
+int ep_plan_launch(const int32_t* counts, int P, int E, int me, int cap, int32_t* dst_base, int32_t* m_loc,
+                   int32_t* status, cudaStream_t stream);
+int ep_push_launch(const void* part0, long long bytes0, const void* part1, long long bytes1, const int32_t* perm,
+                   int k, const int32_t* offsets, const int32_t* dst_base, int R, int E, int P, int me, int cap,
+                   int tokens, void* const* peer0, void* const* peer1, long long* const* peer_tag,
+                   cudaStream_t stream);
+int enable_peer_access(int peer_device);
+int ipc_open(const void* handle_bytes, void** base);
+int ipc_close(void* base);
+int peer_probe(void* peer_ptr, void* local_scratch8);
+
 }  // namespace b200moe

@@ -64,12 +64,28 @@ class CudaOps:
         q, s = self._quant.float8_groupwise_quantize(hidden)
         return [q.view(torch.uint8), s]
 
-    def expert_ffn(self, rows, m_sizes, out_row_map=None, experts=None):
+    def expert_ffn(self, rows, m_sizes, out_row_map=None, experts=None, peer=None):
         """rows: payload tensors sorted by local expert -> [R, H] bf16.  With out_row_map the
         down GEMM stores sorted row r at row out_row_map[r] (leaving expert order in the
-        same pass).  experts=(lo, hi) restricts the call to that range of local experts."""
+        same pass).  experts=(lo, hi) restricts the call to that range of local experts.
+        peer=(tags, bases, n_peers, rows_per_buffer): the down GEMM stores every row into the
+        buffer of the rank named by its tag (nothing is returned)."""
         gg = self._gg
         lo, hi = experts if experts is not None else (0, self.w1.shape[0])
+        if peer is not None:
+            tags, bases, n_peers, y_rows = peer
+            if self.mode == "bf16":
+                h = gg.grouped_gemm(rows[0], self.w1, m_sizes, epilogue="swiglu", check=False,
+                                    cta_group=self.cta_group)
+                return gg.grouped_gemm_ex(gg.KIND_BF16, h, self.w2, m_sizes, cta_group=self.cta_group,
+                                          out_row_tags=tags, peer_bases=bases, n_peers=n_peers, out_rows=y_rows)
+            xq, xs = rows[0].view(torch.float8_e4m3fn), rows[1]
+            h = gg.grouped_gemm_fp8_blockwise(xq, self.w1, m_sizes, xs, self.w1_scale, epilogue="swiglu",
+                                              check=False, cta_group=self.cta_group)
+            hq, hs = self._quant.float8_groupwise_quantize(h)
+            return gg.grouped_gemm_ex(gg.KIND_FP8_BLOCKWISE, hq, self.w2, m_sizes, x_scale=hs, w_scale=self.w2_scale,
+                                      cta_group=self.cta_group, out_row_tags=tags, peer_bases=bases,
+                                      n_peers=n_peers, out_rows=y_rows)
         if self.mode == "bf16":
             h = gg.grouped_gemm(rows[0], self.w1[lo:hi], m_sizes, epilogue="swiglu", check=False,
                                 cta_group=self.cta_group)
@@ -84,6 +100,79 @@ class CudaOps:
 
     def combine(self, y, inv_perm, topk_weights, num_tokens, top_k):
         return self._moe.combine_topk(y, inv_perm, topk_weights, num_tokens, top_k)
+
+    def payload_row_bytes(self, hidden_size):
+        """Bytes per token of each payload part, matching dispatch_payloads."""
+        if self.mode == "bf16":
+            return [2 * hidden_size]
+        return [hidden_size, 4 * (hidden_size // 128)]
+
+
+class PeerBuffers:
+    """This rank's receive side of the peer-memory exchange — payload rows (capacity_rows per
+    part), their (rank, row) tags and the buffer the experts' results come home to — in ONE
+    allocation that every other rank of the group maps with CUDA IPC (opened with its own
+    device current, checked with a copy-engine round trip before any kernel uses it).
+    Built once; every rank must build it at the same time."""
+
+    def __init__(self, group, device, capacity_rows, part_row_bytes, home_rows, hidden_size):
+        import ctypes
+
+        from . import _lib
+        self.P = dist.get_world_size(group)
+        self.me = dist.get_rank(group)
+        self.cap, self.home_rows, self.H = int(capacity_rows), int(home_rows), int(hidden_size)
+        self.part_row_bytes = list(part_row_bytes)
+        sizes = [self.cap * b for b in part_row_bytes] + [self.cap * 8, self.home_rows * self.H * 2]
+        self.offsets, total = [], 0
+        for sz in sizes:
+            self.offsets.append(total)
+            total += (sz + 255) // 256 * 256
+        self.arena = torch.zeros(max(total, 1 << 21), dtype=torch.uint8, device=device)
+        a = self.arena
+        self.parts = [a[o:o + sz] for o, sz in zip(self.offsets[:-2], sizes[:-2])]
+        self.tags = a[self.offsets[-2]:self.offsets[-2] + sizes[-2]].view(torch.int64)
+        self.y_home = a[self.offsets[-1]:self.offsets[-1] + sizes[-1]].view(torch.bfloat16).view(self.home_rows, self.H)
+        # export: (handle of the allocation the arena lives in, byte offset of the arena inside it)
+        shared = a.untyped_storage()._share_cuda_()
+        handle, off_in_block = bytes(shared[1]), int(shared[3]) + a.storage_offset()
+        if len(handle) == 65:      # newer torch prefixes the 64-byte CUDA handle with a one-byte kind tag
+            if handle[:1] != b"c":  # 'c' = plain cudaMalloc memory; anything else cannot be opened this way
+                raise RuntimeError("peer exchange needs cudaMalloc-backed memory (expandable segments are on?)")
+            handle = handle[1:]
+        if len(handle) != 64:
+            raise RuntimeError(f"unexpected CUDA IPC handle length {len(handle)}")
+        gathered = [None] * self.P
+        dist.all_gather_object(gathered, (handle, off_in_block), group=group)
+        lib = _lib.load()
+        self._opened = []
+        scratch = torch.zeros(8, dtype=torch.uint8, device=device)
+        bases = []
+        with torch.cuda.device(device):
+            for r in range(self.P):
+                if r == self.me:
+                    bases.append(a.data_ptr())
+                    continue
+                h, off = gathered[r]
+                base = ctypes.c_void_p()
+                _lib.check(lib.b200moe_ipc_open(h, ctypes.byref(base)), "ipc_open")
+                self._opened.append(base.value)
+                torch.cuda.synchronize()
+                _lib.check(lib.b200moe_peer_probe(base.value + off, scratch.data_ptr()), "peer_probe")
+                bases.append(base.value + off)
+        # device tables of base addresses, one per buffer kind, indexed by rank
+        self.tables = [torch.tensor([bases[r] + o for r in range(self.P)], dtype=torch.int64, device=device)
+                       for o in self.offsets]
+        self.sync = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def close(self):
+        from . import _lib
+        lib = _lib.load()
+        for base in self._opened:
+            lib.b200moe_ipc_close(base)
+        self._opened = []
 
 
 def expert_ids_from_counts(recv_counts, total):
@@ -107,7 +196,14 @@ class ExpertParallelMoE:
                  E / P (it is lowered to the nearest divisor otherwise).
     """
 
-    def __init__(self, ops, num_experts, group=None, waves=1):
+    def __init__(self, ops, num_experts, group=None, waves=1, exchange="nccl", max_tokens=None, top_k=None,
+                 hidden_size=None, capacity_factor=1.5):
+        """exchange="nccl": all_to_all_single collectives (rows land in local buffers first).
+        exchange="peer": rows are written straight into the owner's memory by the sender's push
+        kernel and come home through the down GEMM's store (plain stores over NVLink, CUDA IPC
+        mappings); needs max_tokens (per rank), top_k and hidden_size up front because the
+        shared buffers are built once, and a receive capacity of capacity_factor times the
+        rows a rank sends.  No host synchronisation happens in that mode."""
         self.ops = ops
         self.group = group
         self.E = int(num_experts)
@@ -122,6 +218,59 @@ class ExpertParallelMoE:
         self.e_wave = self.e_local // self.W
         self.last_plan = None
         self._remap = None
+        self.exchange = exchange
+        self.peer = None
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        if exchange == "peer" and self.P > 1:
+            if not (max_tokens and top_k and hidden_size):
+                raise ValueError("exchange='peer' needs max_tokens, top_k and hidden_size")
+            dev = torch.device("cuda", torch.cuda.current_device())
+            home_rows = int(max_tokens) * int(top_k)
+            cap = int(home_rows * float(capacity_factor) + 127) // 128 * 128
+            self.peer = PeerBuffers(group, dev, cap, ops.payload_row_bytes(int(hidden_size)), home_rows,
+                                    int(hidden_size))
+
+    def _forward_peer(self, hidden, topk_weights, topk_ids):
+        """Dispatch by remote stores, return inside the down GEMM; two stream-ordered
+        collectives (1-element all-reduces) order "rows have landed" on every rank."""
+        import ctypes
+
+        from . import _lib
+        from . import groupgemm as gg
+        ops, P, pb = self.ops, self.P, self.peer
+        T, H = hidden.shape
+        k = topk_ids.shape[1]
+        R = T * k
+        if R > pb.home_rows or H != pb.H:
+            raise RuntimeError("more routed rows or another hidden size than the peer buffers were built for")
+        dev = hidden.device
+        lib = _lib.load()
+        stream = torch.cuda.current_stream().cuda_stream
+        word = gg._status_word(dev)
+
+        m_glob, offsets, perm, inv_perm = ops.route(topk_ids, self.E)
+        counts = torch.empty((P, self.E), dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(counts, m_glob, group=self.group)
+        dst_base = torch.empty(self.E, dtype=torch.int32, device=dev)
+        m_loc = torch.empty(self.e_local, dtype=torch.int32, device=dev)
+        _lib.check(lib.b200moe_ep_plan(counts.data_ptr(), P, self.E, pb.me, pb.cap, dst_base.data_ptr(),
+                                       m_loc.data_ptr(), word.data_ptr(), stream), "ep_plan")
+        parts = ops.dispatch_payloads(hidden)
+        p1 = parts[1] if len(parts) > 1 else None
+        rc = lib.b200moe_ep_push(parts[0].data_ptr(), pb.part_row_bytes[0], 0 if p1 is None else p1.data_ptr(),
+                                 pb.part_row_bytes[1] if p1 is not None else 0, perm.data_ptr(), k,
+                                 offsets.data_ptr(), dst_base.data_ptr(), R, self.E, P, pb.me, pb.cap, T,
+                                 pb.tables[0].data_ptr(), pb.tables[1].data_ptr() if p1 is not None else 0,
+                                 pb.tables[len(parts)].data_ptr(), stream)
+        _lib.check(rc, "ep_push")
+        dist.all_reduce(pb.sync, group=self.group)          # every rank's rows have landed everywhere
+        rows = []
+        for buf, nbytes, part in zip(pb.parts, pb.part_row_bytes, parts):
+            rows.append(buf.view(part.dtype).view(pb.cap, nbytes // part.element_size()))
+        ops.expert_ffn(rows, m_loc, peer=(pb.tags, pb.tables[len(parts) + 1], P, pb.home_rows))
+        dist.all_reduce(pb.sync, group=self.group)          # every result row is home
+        return ops.combine(pb.y_home[:R], inv_perm, topk_weights, T, k)
 
     def _key_table(self, device):
         """Sort key of every global expert: (wave, destination rank, expert inside the wave), so
@@ -151,6 +300,9 @@ class ExpertParallelMoE:
             y_home = ops.expert_ffn(rows, m_glob)
             self.last_plan = {"send_splits": [int(topk_ids.numel())], "recv_splits": [int(topk_ids.numel())]}
             return ops.combine(y_home, inv_perm, topk_weights, T, k)
+
+        if self.peer is not None:
+            return self._forward_peer(hidden, topk_weights, topk_ids)
 
         # 1. sort this rank's routed rows by (wave, destination rank, expert)
         keys = self._key_table(dev)[topk_ids.reshape(-1).long()]

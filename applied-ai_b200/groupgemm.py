@@ -199,3 +199,49 @@ def grouped_gemm_fp8_blockwise(x, w, m_sizes, x_scale, w_scale, *, epilogue="non
     if _default_check if check is None else check:
         raise_on_status(word, "grouped_gemm_fp8_blockwise")
     return y
+
+
+KIND_BF16, KIND_FP8_ROWWISE, KIND_FP8_BLOCKWISE = 0, 1, 2
+
+
+def grouped_gemm_ex(kind, x, w, m_sizes, *, x_scale=None, w_scale=None, epilogue="none", cta_group=0, y=None,
+                    out_row_map=None, out_row_tags=None, peer_bases=None, n_peers=0, out_rows=None, check=False):
+    """Struct-described grouped GEMM (b200moe_grouped_gemm_ex).  Besides everything the plain
+    entry points do, result rows can be sent to (rank, row) destinations: out_row_tags int64 [M]
+    = (rank << 32) | row and peer_bases = int64 device tensor of n_peers base addresses of bf16
+    buffers with out_rows rows each (this rank's own buffer included).  Returns y, or None when
+    rows go to peer buffers."""
+    import ctypes
+    m_sizes, G, M, N, K = _prepare(x, w, m_sizes, torch.bfloat16 if kind == KIND_BF16 else torch.float8_e4m3fn)
+    epi = {"none": 0, "swiglu": 1}[epilogue]
+    n_out = N // 2 if epi == 1 else N
+    d = _lib.GemmDesc()
+    d.x, d.w, d.m_sizes = x.data_ptr(), w.data_ptr(), m_sizes.data_ptr()
+    d.x_scale = 0 if x_scale is None else x_scale.data_ptr()
+    d.w_scale = 0 if w_scale is None else w_scale.data_ptr()
+    d.M, d.N, d.K, d.G = M, N, K, G
+    d.ldy, d.y_col_group_stride = n_out, 0
+    d.kind, d.epilogue, d.cta_group = kind, epi, cta_group
+    word = _status_word(x.device)
+    d.status = word.data_ptr()
+    if out_row_tags is not None:
+        _require(out_row_tags.dtype == torch.int64 and out_row_tags.is_contiguous() and out_row_tags.numel() >= M,
+                 "out_row_tags must be a contiguous int64 tensor with one entry per row of x")
+        _require(peer_bases is not None and peer_bases.dtype == torch.int64 and n_peers > 0 and out_rows,
+                 "peer_bases (int64 device tensor), n_peers and out_rows are needed with out_row_tags")
+        d.y_row_tags, d.y_peer_bases, d.n_peers, d.y_rows = out_row_tags.data_ptr(), peer_bases.data_ptr(), n_peers, out_rows
+        d.y = peer_bases.data_ptr()  # not dereferenced as y; must be non-null
+    else:
+        if y is None:
+            y = torch.empty((M if out_rows is None else out_rows, n_out), device=x.device, dtype=torch.bfloat16)
+        d.y = y.data_ptr()
+        if out_row_map is not None:
+            d.y_row_map, d.y_rows = _row_map_args(out_row_map, y, x.device)
+    if M > 0:
+        lib = _lib.load()
+        with torch.cuda.device(x.device):
+            rc = lib.b200moe_grouped_gemm_ex(ctypes.addressof(d), torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "grouped_gemm_ex")
+        if check:
+            raise_on_status(word, "grouped_gemm_ex")
+    return None if out_row_tags is not None else y

@@ -478,7 +478,8 @@ def run_layer(args):
     ops = CudaOps(w1, w2, mode=mode, cta_group=args.cta_group)
     if mode != "bf16":
         del w1, w2
-    layer = ExpertParallelMoE(ops, E, waves=args.waves)
+    layer = ExpertParallelMoE(ops, E, waves=args.waves, exchange=args.exchange, max_tokens=t_loc, top_k=k,
+                              hidden_size=H, capacity_factor=1.25)
 
     def step(h=hidden):
         return layer(h, topk_w, topk_ids)
@@ -596,7 +597,10 @@ def run_layer(args):
             "config": {"workload": f"{args.workload}: MoE FFN layer T={T} H={H} I={I} E={E} top-{k} {mode}, "
                                    f"{t_loc} tokens and {e_loc} experts per GPU",
                        "l2": "weights per GPU exceed the 126 MiB L2",
-                       "exchange": f"NCCL all_to_all_single (counts, payload, return), {layer.W} waves" if world > 1 else "none (1 GPU)"},
+                       "exchange": ("none (1 GPU)" if world == 1 else
+                                    f"NCCL all_to_all_single (counts, payload, return), {layer.W} waves"
+                                    if args.exchange == "nccl" else
+                                    "peer memory: push kernel + down-GEMM stores over NVLink, 2 one-element all-reduces")},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
                          "frac": per_gpu / peak, "traffic": args.traffic, "peak_source": src,
                          "note": "whole layer (route, gather, 2 GEMMs, quantise, combine, exchange) against the GEMM peak"},
@@ -690,6 +694,8 @@ def main():
     ap.add_argument("--cta-group", type=int, default=0, dest="cta_group")
     ap.add_argument("--waves", type=int, default=2,
                     help="expert-parallel layers: chunks of local experts whose exchange overlaps compute")
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
+                    help="expert-parallel layers: NCCL all-to-all, or remote stores into peer memory")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture, echoed into the roofline object")
     args = ap.parse_args()

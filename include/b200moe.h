@@ -39,6 +39,7 @@ typedef void* b200moe_stream_t;
 #define B200MOE_STIMEOUT_FIRST 16  /* 16..19: a bounded wait inside the GEMM kernel ran out */
 #define B200MOE_STIMEOUT_LAST 19
 #define B200MOE_SSELFTEST 20       /* b200moe_selftest_wait_timeout: the unsatisfied wait ran out, as it should */
+#define B200MOE_SCAPACITY 24       /* expert-parallel dispatch: a receive buffer is too small for the routed rows */
 #define B200MOE_SWRONGARCH 32
 
 /* flags of the grouped GEMM entry points */
@@ -88,6 +89,65 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
                                        int64_t y_col_group_stride, int epilogue, int cta_group,
                                        const int32_t* y_row_map, int y_rows, int32_t* status,
                                        b200moe_stream_t stream);
+
+/* One grouped GEMM described by a struct: everything the three entry points above can do,
+ * plus a second way to place result rows — y_row_tags[r] = (rank << 32) | row sends result
+ * row r to row `row` of y_peer_bases[rank] (bf16, pitch ldy, y_rows rows each), which may
+ * be another GPU's memory mapped into this process: the return leg of the expert-parallel
+ * exchange happens inside the GEMM's store, as plain stores over NVLink.  No counterpart
+ * in the reference (it has no distributed code). */
+#define B200MOE_KIND_BF16 0
+#define B200MOE_KIND_FP8_ROWWISE 1
+#define B200MOE_KIND_FP8_BLOCKWISE 2
+typedef struct b200moe_gemm_desc {
+    const void* x;            /* [M, K] */
+    const void* w;            /* [G, N, K] */
+    const int32_t* m_sizes;   /* [G] device */
+    void* y;                  /* bf16 output (unused when y_row_tags is set) */
+    const float* x_scale;     /* FP8 kinds */
+    const float* w_scale;
+    int M, N, K, G;
+    int64_t ldy, y_col_group_stride;
+    int kind;                 /* B200MOE_KIND_* */
+    int epilogue;             /* B200MOE_EPI_* */
+    int cta_group;
+    int y_rows;               /* rows of the destination buffer(s) when a map or tags are given */
+    const int32_t* y_row_map; /* optional */
+    const int64_t* y_row_tags;/* optional, excludes y_row_map */
+    void* const* y_peer_bases;/* device array of n_peers base pointers */
+    int n_peers;
+    int32_t* status;
+} b200moe_gemm_desc;
+int b200moe_grouped_gemm_ex(const b200moe_gemm_desc* desc, b200moe_stream_t stream);
+
+/* Expert-parallel dispatch over peer memory (no counterpart in the reference).
+ * b200moe_ep_plan: from counts[P][E] (rows every rank routes to every global expert, after
+ * an all-gather) compute, for rank my_rank, dst_base[E] = first row in the owner's receive
+ * buffer for my rows of each expert, and m_local[E/P] = rows this rank receives per local
+ * expert.  Order on the owner: expert, then source rank, then source order.  Sets status
+ * B200MOE_SCAPACITY if some rank would receive more than capacity_rows rows.
+ * b200moe_ep_push: for every routed row p (sorted by global expert: perm, offsets from
+ * b200moe_route) copy its token's bytes (part0 and optionally part1, row sizes multiples of
+ * 16) into the owner's buffers peer_part0[d] / peer_part1[d] at row dst_base[e] + i and
+ * write peer_tags[d][row] = (my_rank << 32) | p.  Rows past capacity_rows are dropped.
+ * The peer_* arrays are DEVICE arrays of P pointers into buffers of capacity_rows rows on
+ * each rank, mapped into this process (CUDA IPC); call b200moe_enable_peer_access for each
+ * peer device once.  The caller orders "all pushes done" before the GEMMs with a
+ * collective on the stream. */
+int b200moe_ep_plan(const int32_t* counts, int P, int E, int my_rank, int capacity_rows, int32_t* dst_base,
+                    int32_t* m_local, int32_t* status, b200moe_stream_t stream);
+int b200moe_ep_push(const void* part0, int64_t row_bytes0, const void* part1, int64_t row_bytes1,
+                    const int32_t* perm, int top_k, const int32_t* offsets, const int32_t* dst_base, int R, int E,
+                    int P, int my_rank, int capacity_rows, int tokens, void* const* peer_part0,
+                    void* const* peer_part1, int64_t* const* peer_tags, b200moe_stream_t stream);
+int b200moe_enable_peer_access(int peer_device);
+/* Map a buffer another rank exported with cudaIpcGetMemHandle (64-byte handle) into this
+ * process; call with this rank's device current.  b200moe_peer_probe copies one word into
+ * the mapped buffer and back with the copy engine (synchronous, set-up time only) and
+ * returns 0 when the mapping works; local_scratch8 is 8 bytes of this rank's device memory. */
+int b200moe_ipc_open(const void* handle64, void** base);
+int b200moe_ipc_close(void* base);
+int b200moe_peer_probe(void* peer_ptr, void* local_scratch8);
 
 /* Dense D = alpha * A @ B^T + beta * C with the grouped kernel's G = 1 mode.
  * A [M,K], B [N,K] IEEE half (float16), C and D [M,N] float32, row-major; C may be NULL

@@ -62,7 +62,7 @@ def test_single_rank_fp8_blockwise_layer():
     assert O.rel_err(out.cpu().float(), ref) <= FP8_REL_TOL
 
 
-def _worker(rank, world, port, mode, waves, ret):
+def _worker(rank, world, port, mode, waves, ret, exchange="nccl"):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
@@ -75,7 +75,13 @@ def _worker(rank, world, port, mode, waves, ret):
         tl, el = T // world, E // world
         sl = slice(rank * tl, (rank + 1) * tl)
         ops = CudaOps(w1[rank * el:(rank + 1) * el].to(d), w2[rank * el:(rank + 1) * el].to(d), mode, cta_group=2)
-        out = ExpertParallelMoE(ops, E, waves=waves)(hidden[sl].to(d), tw[sl].to(d), ids[sl].to(d))
+        layer = ExpertParallelMoE(ops, E, waves=waves, exchange=exchange, max_tokens=tl, top_k=k, hidden_size=H)
+        out = layer(hidden[sl].to(d), tw[sl].to(d), ids[sl].to(d))
+        if exchange == "peer":   # the shared buffers are reused from call to call
+            out2 = layer(hidden[sl].to(d), tw[sl].to(d), ids[sl].to(d))
+            assert torch.equal(out, out2)
+            from applied_ai_b200 import groupgemm
+            assert int(groupgemm._status_word(d).item()) == 0
         torch.cuda.synchronize()
         ret[rank] = out.cpu()
     finally:
@@ -97,3 +103,20 @@ def test_two_ranks_equal_one_rank_bit_for_bit(mode, waves):
     one = ExpertParallelMoE(CudaOps(w1.to(d), w2.to(d), mode, cta_group=2), 8)(hidden.to(d), tw.to(d), ids.to(d)).cpu()
     two = torch.cat([ret[0], ret[1]])
     assert torch.equal(one, two)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("mode", ["bf16", "fp8_blockwise"])
+def test_peer_memory_exchange_equals_one_rank_bit_for_bit(mode):
+    """Dispatch by remote stores and return inside the down GEMM's store, against the single-rank layer."""
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, port, mode, 1, ret, "peer"), nprocs=2, join=True)
+    hidden, w1, w2, tw, ids = problem(512, 256, 256, 8, 2, 3)
+    d = "cuda"
+    one = ExpertParallelMoE(CudaOps(w1.to(d), w2.to(d), mode, cta_group=2), 8)(hidden.to(d), tw.to(d), ids.to(d)).cpu()
+    assert torch.equal(one, torch.cat([ret[0], ret[1]]))
