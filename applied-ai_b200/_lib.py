@@ -50,6 +50,7 @@ SIGNATURES = {
     "b200moe_ep_push": [_c_vp, _c_i64, _c_vp, _c_i64, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
                         _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp],
     "b200moe_enable_peer_access": [_c_int],
+    "b200moe_ipc_export": [_c_vp, _c_vp, ctypes.POINTER(ctypes.c_uint64)],
     "b200moe_ipc_open": [_c_vp, ctypes.POINTER(_c_vp)],
     "b200moe_ipc_close": [_c_vp],
     "b200moe_peer_probe": [_c_vp, _c_vp],

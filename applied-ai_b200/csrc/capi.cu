@@ -170,6 +170,12 @@ int b200moe_ep_push(const void* part0, int64_t row_bytes0, const void* part1, in
 
 int b200moe_enable_peer_access(int peer_device) { return enable_peer_access(peer_device); }
 int b200moe_ipc_open(const void* handle64, void** base) { return ipc_open(handle64, base); }
+int b200moe_ipc_export(const void* dev_ptr, void* handle_out64, uint64_t* offset_out) {
+    unsigned long long off = 0;
+    const int rc = ipc_export(dev_ptr, handle_out64, &off);
+    if (rc == 0) *offset_out = off;
+    return rc;
+}
 int b200moe_ipc_close(void* base) { return ipc_close(base); }
 int b200moe_peer_probe(void* peer_ptr, void* local_scratch8) { return peer_probe(peer_ptr, local_scratch8); }
 

@@ -10,6 +10,7 @@
 //   row(dest d, local expert e, i-th row of mine)
 //       = sum_{e' < e} total[d][e']  +  sum_{s < me} C[s][d*El + e]  +  i
 // which is the stable (expert, source rank, source order) ordering.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
@@ -156,6 +157,28 @@ int ipc_open(const void* handle_bytes, void** base) {
     cudaIpcMemHandle_t h;
     memcpy(&h, handle_bytes, sizeof(h));
     return static_cast<int>(cudaIpcOpenMemHandle(base, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+// Export side: the handle of the cudaMalloc allocation that contains dev_ptr, and the byte
+// offset of dev_ptr inside that allocation (the importer gets the allocation's base back).
+int ipc_export(const void* dev_ptr, void* handle_out64, unsigned long long* offset_out) {
+    if (dev_ptr == nullptr || handle_out64 == nullptr || offset_out == nullptr) return kErrBadArgument;
+    using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || sym == nullptr)
+        return kErrNoDriverEntry;
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (reinterpret_cast<RangeFn>(sym)(&base, &size, reinterpret_cast<CUdeviceptr>(dev_ptr)) != CUDA_SUCCESS)
+        return kErrBadArgument;
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    memcpy(handle_out64, &h, sizeof(h));
+    *offset_out = static_cast<unsigned long long>(reinterpret_cast<CUdeviceptr>(dev_ptr) - base);
+    return 0;
 }
 
 int ipc_close(void* base) { return static_cast<int>(cudaIpcCloseMemHandle(base)); }

@@ -38,6 +38,7 @@ int ep_push_launch(const void* part0, long long bytes0, const void* part1, long 
                    cudaStream_t stream);
 int enable_peer_access(int peer_device);
 int ipc_open(const void* handle_bytes, void** base);
+int ipc_export(const void* dev_ptr, void* handle_out64, unsigned long long* offset_out);
 int ipc_close(void* base);
 int peer_probe(void* peer_ptr, void* local_scratch8);
 

@@ -134,17 +134,14 @@ class PeerBuffers:
         self.tags = a[self.offsets[-2]:self.offsets[-2] + sizes[-2]].view(torch.int64)
         self.y_home = a[self.offsets[-1]:self.offsets[-1] + sizes[-1]].view(torch.bfloat16).view(self.home_rows, self.H)
         # export: (handle of the allocation the arena lives in, byte offset of the arena inside it)
-        shared = a.untyped_storage()._share_cuda_()
-        handle, off_in_block = bytes(shared[1]), int(shared[3]) + a.storage_offset()
-        if len(handle) == 65:      # newer torch prefixes the 64-byte CUDA handle with a one-byte kind tag
-            if handle[:1] != b"c":  # 'c' = plain cudaMalloc memory; anything else cannot be opened this way
-                raise RuntimeError("peer exchange needs cudaMalloc-backed memory (expandable segments are on?)")
-            handle = handle[1:]
-        if len(handle) != 64:
-            raise RuntimeError(f"unexpected CUDA IPC handle length {len(handle)}")
+        lib = _lib.load()
+        hbuf = ctypes.create_string_buffer(64)
+        off = ctypes.c_uint64(0)
+        with torch.cuda.device(device):
+            _lib.check(lib.b200moe_ipc_export(a.data_ptr(), hbuf, ctypes.byref(off)), "ipc_export")
+        handle, off_in_block = hbuf.raw, int(off.value)
         gathered = [None] * self.P
         dist.all_gather_object(gathered, (handle, off_in_block), group=group)
-        lib = _lib.load()
         self._opened = []
         scratch = torch.zeros(8, dtype=torch.uint8, device=device)
         bases = []

@@ -141,10 +141,12 @@ int b200moe_ep_push(const void* part0, int64_t row_bytes0, const void* part1, in
                     int P, int my_rank, int capacity_rows, int tokens, void* const* peer_part0,
                     void* const* peer_part1, int64_t* const* peer_tags, b200moe_stream_t stream);
 int b200moe_enable_peer_access(int peer_device);
-/* Map a buffer another rank exported with cudaIpcGetMemHandle (64-byte handle) into this
+/* b200moe_ipc_export: the 64-byte IPC handle of the cudaMalloc allocation containing dev_ptr
+ * and dev_ptr's byte offset in it.  b200moe_ipc_open: map such an allocation into this
  * process; call with this rank's device current.  b200moe_peer_probe copies one word into
  * the mapped buffer and back with the copy engine (synchronous, set-up time only) and
  * returns 0 when the mapping works; local_scratch8 is 8 bytes of this rank's device memory. */
+int b200moe_ipc_export(const void* dev_ptr, void* handle_out64, uint64_t* offset_out);
 int b200moe_ipc_open(const void* handle64, void** base);
 int b200moe_ipc_close(void* base);
 int b200moe_peer_probe(void* peer_ptr, void* local_scratch8);
