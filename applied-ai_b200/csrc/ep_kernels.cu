@@ -93,10 +93,17 @@ ep_push_kernel(const uint8_t* __restrict__ part0, long long bytes0, const uint8_
             for (; v < n; v += 32) dst[v] = __ldg(src + v);
         }
         if (part1 != nullptr) {
-            const uint4* src = reinterpret_cast<const uint4*>(part1 + static_cast<size_t>(tok) * bytes1);
-            uint4* dst = reinterpret_cast<uint4*>(peer1[d] + static_cast<size_t>(row) * bytes1);
-            const int n = static_cast<int>(bytes1 >> 4);
-            for (int v = lane; v < n; v += 32) dst[v] = __ldg(src + v);
+            if ((bytes1 & 15) == 0) {
+                const uint4* src = reinterpret_cast<const uint4*>(part1 + static_cast<size_t>(tok) * bytes1);
+                uint4* dst = reinterpret_cast<uint4*>(peer1[d] + static_cast<size_t>(row) * bytes1);
+                const int n = static_cast<int>(bytes1 >> 4);
+                for (int v = lane; v < n; v += 32) dst[v] = __ldg(src + v);
+            } else {  // short rows (a few scales): 4 bytes at a time
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(part1 + static_cast<size_t>(tok) * bytes1);
+                uint32_t* dst = reinterpret_cast<uint32_t*>(peer1[d] + static_cast<size_t>(row) * bytes1);
+                const int n = static_cast<int>(bytes1 >> 2);
+                for (int v = lane; v < n; v += 32) dst[v] = __ldg(src + v);
+            }
         }
         if (lane == 0) peer_tag[d][row] = (static_cast<long long>(me) << 32) | static_cast<long long>(p);
     }
@@ -118,9 +125,10 @@ int ep_push_launch(const void* part0, long long bytes0, const void* part1, long 
                    cudaStream_t stream) {
     if (part0 == nullptr || perm == nullptr || offsets == nullptr || dst_base == nullptr || peer0 == nullptr ||
         peer_tag == nullptr || k <= 0 || R < 0 || E <= 0 || P <= 0 || E % P != 0 || bytes0 <= 0 || (bytes0 & 15) ||
-        (part1 != nullptr && (peer1 == nullptr || bytes1 <= 0 || (bytes1 & 15))))
+        (part1 != nullptr && (peer1 == nullptr || bytes1 <= 0 || (bytes1 & 3))))
         return kErrBadArgument;
     if ((reinterpret_cast<uintptr_t>(part0) & 15u) || (reinterpret_cast<uintptr_t>(part1) & 15u)) return kErrAlignment;
+    // rows of part 1 start at multiples of bytes1 inside 256-byte aligned buffers: 4-byte aligned at least
     if (R == 0) return 0;
     int blocks = (R + 7) / 8;
     if (blocks > 148 * 8) blocks = 148 * 8;

@@ -20,13 +20,16 @@ constexpr int kABytes = kRowsPerCta * kRowBytes;    // 16 KiB
 constexpr int kSubBoxBytes = 128 * kRowBytes;       // a 128-row box of w: 16 KiB
 constexpr int kTmemCols = 2 * kTileN;               // two accumulators
 
-template <int CTAS>
+// LESS = stages given up (each kernel trades ring depth against epilogue staging space).
+template <int CTAS, int LESS = 0>
 struct StageCfg {
     static constexpr int kBBytes = (2 / CTAS) * kSubBoxBytes;  // this CTA's share of the w box
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = CTAS == 1 ? 4 : 6;
-    static constexpr int kRingBytes = kStages * kStageBytes;   // 192 KiB either way
+    static constexpr int kStages = (CTAS == 1 ? 4 : 6) - LESS;
+    static constexpr int kRingBytes = kStages * kStageBytes;   // 192 KiB at full depth
 };
+
+constexpr int kWarpStageBytes = 32 * 128;  // epilogue staging per warp: 32 rows x 128 bytes
 
 struct SmemTail {
     uint64_t full[8];
@@ -41,23 +44,74 @@ struct SmemTail {
     int tile_off[kMaxGroups + 1];
 };
 
-template <int CTAS>
+template <int CTAS, int LESS, int STAGING_BYTES>
 constexpr size_t gg_smem_bytes() {
-    return 1024 + StageCfg<CTAS>::kRingBytes + sizeof(SmemTail);
+    return 1024 + StageCfg<CTAS, LESS>::kRingBytes + sizeof(SmemTail) + 16 + STAGING_BYTES;
 }
 
 // Carves the dynamic shared memory: a 1024-byte aligned stage ring followed by the tail.
 struct SmemView {
     uint32_t ring_addr;
     SmemTail* tail;
+    uint4* warp_stage;  // EPI_WARPS x kWarpStageBytes, 16-byte aligned
 };
-template <int CTAS>
+template <int CTAS, int LESS>
 __device__ __forceinline__ SmemView carve_smem(uint8_t* smem_raw) {
     const uint32_t raw_addr = smem_u32(smem_raw);
     SmemView v;
     v.ring_addr = (raw_addr + 1023u) & ~1023u;
-    v.tail = reinterpret_cast<SmemTail*>(smem_raw + (v.ring_addr - raw_addr) + StageCfg<CTAS>::kRingBytes);
+    uint8_t* tail = smem_raw + (v.ring_addr - raw_addr) + StageCfg<CTAS, LESS>::kRingBytes;
+    v.tail = reinterpret_cast<SmemTail*>(tail);
+    v.warp_stage = reinterpret_cast<uint4*>(tail + ((sizeof(SmemTail) + 15) & ~size_t(15)));
     return v;
+}
+
+// ---- epilogue staging, used when rows go to ANOTHER GPU: a warp parks 32 rows x 128 bytes
+// (lane = row) in shared memory and writes them out again row by row, so that one store
+// instruction covers whole 128-byte runs of 4 rows instead of 16 bytes of 32 different rows
+// (NVLink carries 16-byte writes poorly).  For local memory the direct stores below are
+// faster: the extra shared-memory traffic competes with the MMA's operand reads.  16-byte chunks are XOR-swizzled by
+// row so neither direction has bank conflicts.
+// RUN = bytes per staged row (128 or 64); a warp's buffer is 32 * RUN bytes.
+template <int RUN = 128>
+__device__ __forceinline__ void stage_put(uint4* stage, int lane, int chunk, uint4 v) {
+    constexpr int kChunks = RUN / 16;
+    stage[lane * kChunks + (chunk ^ (lane & (kChunks - 1)))] = v;
+}
+__device__ __forceinline__ char* shfl_ptr(char* p, int src_lane) {
+    const unsigned long long v = reinterpret_cast<unsigned long long>(p);
+    const unsigned lo = __shfl_sync(0xffffffffu, static_cast<unsigned>(v), src_lane);
+    const unsigned hi = __shfl_sync(0xffffffffu, static_cast<unsigned>(v >> 32), src_lane);
+    return reinterpret_cast<char*>((static_cast<unsigned long long>(hi) << 32) | lo);
+}
+// my_dst: where this lane's row (row = lane) starts its 128-byte run, or nullptr to skip the
+// row.  valid_bytes (warp-uniform): how much of the run lies inside the output's columns.
+// ELEM: bytes per element, for the ragged last chunk and for unaligned destinations.
+template <int ELEM, int RUN = 128>
+__device__ __forceinline__ void stage_flush(const uint4* stage, int lane, char* my_dst, int valid_bytes) {
+    constexpr int kChunks = RUN / 16;            // 16-byte chunks per row
+    constexpr int kRowsPerStep = 32 / kChunks;   // rows covered by one store instruction
+#pragma unroll
+    for (int i = 0; i < 32 / kRowsPerStep; ++i) {
+        const int r = i * kRowsPerStep + lane / kChunks;
+        const int c = lane % kChunks;
+        char* dst = shfl_ptr(my_dst, r);
+        if (dst == nullptr || c * 16 >= valid_bytes) continue;
+        const uint4 v = stage[r * kChunks + (c ^ (r & (kChunks - 1)))];
+        dst += c * 16;
+        if (c * 16 + 16 <= valid_bytes && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+            *reinterpret_cast<uint4*>(dst) = v;
+        } else {
+            const int n = min(16, valid_bytes - c * 16) / ELEM;
+            if constexpr (ELEM == 2) {
+                const unsigned short* e = reinterpret_cast<const unsigned short*>(&v);
+                for (int j = 0; j < n; ++j) reinterpret_cast<unsigned short*>(dst)[j] = e[j];
+            } else {
+                const unsigned* e = reinterpret_cast<const unsigned*>(&v);
+                for (int j = 0; j < n; ++j) reinterpret_cast<unsigned*>(dst)[j] = e[j];
+            }
+        }
+    }
 }
 
 __device__ __forceinline__ void report(int32_t* status, int code) {
@@ -117,8 +171,9 @@ __device__ __forceinline__ bool resolve_row_dest(const GGParams& p, int row, boo
     return true;
 }
 
-// Stores 32 consecutive fp32 values of one output row as bf16 at columns [col, col+32),
-// clipped to n_out columns; 16-byte stores when the run is whole and aligned.
+// Direct store of 32 consecutive fp32 values of one output row as bf16 at columns
+// [col, col+32), clipped to n_out columns; 16-byte stores when the run is whole and aligned.
+// Used for local memory, where L2 merges the partial lines of neighbouring rows.
 __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* y_row, int col, int n_out, const float* f) {
     if (col >= n_out) return;
     __nv_bfloat16* dst = y_row + col;
@@ -139,11 +194,33 @@ __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* y_row, int col, i
             if (col + j < n_out) dst[j] = __float2bfloat16_rn(f[j]);
     }
 }
+// Same for the fp32 output alpha * acc + beta * C (c_row may be nullptr when beta == 0).
+__device__ __forceinline__ void store_row_chunk_axpby(float* d_row, const float* c_row, int col, int n_out,
+                                                      const float* f, float alpha, float beta) {
+    if (col >= n_out) return;
+    float* dst = d_row + col;
+    const float* c = c_row != nullptr ? c_row + col : nullptr;
+    if ((col + 32 <= n_out) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) &&
+        ((reinterpret_cast<uintptr_t>(c) & 15u) == 0)) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            float4 cv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c != nullptr) cv = __ldg(reinterpret_cast<const float4*>(c) + q);
+            reinterpret_cast<float4*>(dst)[q] =
+                make_float4(alpha * f[q * 4 + 0] + beta * cv.x, alpha * f[q * 4 + 1] + beta * cv.y,
+                            alpha * f[q * 4 + 2] + beta * cv.z, alpha * f[q * 4 + 3] + beta * cv.w);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col + j < n_out) dst[j] = alpha * f[j] + (c != nullptr ? beta * c[j] : 0.0f);
+    }
+}
 
 // Run by ONE warp: exclusive prefix sums of rows and tiles over the groups (32 groups per
 // step), validation of m_sizes, and initialisation of the barriers.  `acc_empty_count` is
 // the number of arrivals that hand an accumulator back to the MMA issuer.
-template <int CTAS>
+template <int CTAS, int LESS>
 __device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GGParams& p, int lane, int tile_rows,
                                                           int acc_empty_count) {
     int row_carry = 0, tile_carry = 0, bad = 0;
@@ -181,7 +258,7 @@ __device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GG
         st->total_tiles = bad ? 0 : tile_carry;
         st->invalid = bad;
         if (bad) report(p.status, kStatusBadGroupSizes);
-        for (int s = 0; s < StageCfg<CTAS>::kStages; ++s) {
+        for (int s = 0; s < StageCfg<CTAS, LESS>::kStages; ++s) {
             mbar_init(&st->full[s], 1);
             mbar_init(&st->empty[s], 1);
         }
@@ -196,11 +273,11 @@ __device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GG
 // TMA producer, run by ONE thread per CTA: for every tile of this cluster and every
 // 128-byte slice of K, wait for a free stage and fetch this CTA's 128 rows of x and its
 // share of the tile's two 128-row boxes of w[g] (rows nb0.. and nb1..).
-template <int CTAS, bool SWIGLU>
+template <int CTAS, int LESS, bool SWIGLU>
 __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUtensorMap* tm_w, SmemTail* st,
                                               uint32_t ring_addr, const GGParams& p, uint32_t cta_rank,
                                               int cluster_id, int num_clusters, int elems_per_stage, int num_kb) {
-    using Cfg = StageCfg<CTAS>;
+    using Cfg = StageCfg<CTAS, LESS>;
     constexpr int kTileRows = kRowsPerCta * CTAS;
     constexpr uint32_t kTxBytes = static_cast<uint32_t>(Cfg::kStageBytes) * CTAS;
     volatile int* abort_flag = &st->abort_flag;

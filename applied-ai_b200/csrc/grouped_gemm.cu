@@ -38,13 +38,13 @@ template <int ELEM_BYTES, int CTAS, int SCALE, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GGParams p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
-    using Cfg = StageCfg<CTAS>;
+    using Cfg = StageCfg<CTAS, 0>;
     constexpr bool kFp8 = ELEM_BYTES == 1;
     constexpr int kElemsPerStage = kRowBytes / ELEM_BYTES;  // K elements per stage
     constexpr int kTileRows = kRowsPerCta * CTAS;
 
     extern __shared__ uint8_t smem_raw[];
-    const SmemView sv = carve_smem<CTAS>(smem_raw);
+    const SmemView sv = carve_smem<CTAS, 0>(smem_raw);
     const uint32_t ring_addr = sv.ring_addr;
     SmemTail* st = sv.tail;
     volatile int* abort_flag = &st->abort_flag;
@@ -62,7 +62,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
     }
     __syncthreads();
     if (warp == 0) {
-        build_tables_and_barriers<CTAS>(st, p, lane, kTileRows, kEpiWarps * CTAS);
+        build_tables_and_barriers<CTAS, 0>(st, p, lane, kTileRows, kEpiWarps * CTAS);
         if (lane == 0) {
             prefetch_tensormap(&tm_x);
             prefetch_tensormap(&tm_w);
@@ -83,7 +83,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
     if (warp == 0) {
         // ================= TMA producer (one thread per CTA)
         if (lane == 0)
-            producer_loop<CTAS, EPI == 1>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters,
+            producer_loop<CTAS, 0, EPI == 1>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters,
                                           kElemsPerStage, num_kb);
     } else if (warp == 1) {
         // ================= MMA issuer (one thread of the leader CTA)
@@ -152,87 +152,80 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
             if constexpr (SCALE == 1) x_scale = row_ok ? p.x_scale[row] : 0.0f;
 
             constexpr int kOutCols = EPI == 1 ? 128 : kTileN;  // output columns per tile
+            constexpr int kOutElem = EPI == 2 ? 4 : 2;         // bytes per output element
+            constexpr int kSlabCols = 128 / kOutElem;          // columns in one 128-byte staged run
             const int col0 = tc.n_idx * kOutCols;              // first output column of the tile (within group)
             // Destination row: the row itself, where the caller's row map sends it, or a row of
             // another rank's buffer.
             RowDest rd;
             const bool store_ok = resolve_row_dest(p, row, row_ok, &rd);
-            const long long drow = rd.drow;
-            __nv_bfloat16* const y_row =
-                rd.base + static_cast<size_t>(drow) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
+            char* const my_row = store_ok ? reinterpret_cast<char*>(rd.base) +
+                                                (static_cast<size_t>(rd.drow) * p.ldy +
+                                                 static_cast<size_t>(tc.g) * p.y_col_group_stride) * kOutElem
+                                          : nullptr;
+            const char* const my_c =
+                (EPI == 2 && store_ok && p.beta != 0.0f)
+                    ? reinterpret_cast<const char*>(p.c_in) + static_cast<size_t>(rd.drow) * p.ldy * sizeof(float)
+                    : nullptr;
             const float* const w_scale_g = SCALE == 1 ? p.w_scale + static_cast<size_t>(tc.g) * p.N : nullptr;
+            uint4* const stage = sv.warp_stage + (warp - 2) * (kWarpStageBytes / 16);
+            const bool to_peers = p.row_tags != nullptr;  // kernel-uniform
 
 #pragma unroll 1
-            for (int c = 0; c < kOutCols / 32; ++c) {
-                const int col = col0 + c * 32;
-                if (col >= p.n_out) break;  // warp-uniform: nothing left to store in this tile
-                uint32_t v[32];
-                float f[32];
-                tmem_ld_32x32(t_acc + static_cast<uint32_t>(c * 32), v);
-                if constexpr (EPI == 1) {
-                    uint32_t u[32];
-                    tmem_ld_32x32(t_acc + static_cast<uint32_t>(128 + c * 32), u);
-                    tmem_ld_wait(v);
-                    tmem_ld_wait(u);
+            for (int slab = 0; slab < kOutCols / kSlabCols; ++slab) {
+                const int scol = col0 + slab * kSlabCols;
+                if (scol >= p.n_out) break;  // warp-uniform: nothing left to store in this tile
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] = silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j]));
-                } else {
-                    tmem_ld_wait(v);
+                for (int part = 0; part < kSlabCols / 32; ++part) {
+                    const int c = slab * (kSlabCols / 32) + part;  // 32-column chunk inside the tile
+                    const int col = col0 + c * 32;
+                    uint32_t v[32];
+                    float f[32];
+                    tmem_ld_32x32(t_acc + static_cast<uint32_t>(c * 32), v);
+                    if constexpr (EPI == 1) {
+                        uint32_t u[32];
+                        tmem_ld_32x32(t_acc + static_cast<uint32_t>(128 + c * 32), u);
+                        tmem_ld_wait(v);
+                        tmem_ld_wait(u);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                }
-                if constexpr (SCALE == 1) {
+                        for (int j = 0; j < 32; ++j) f[j] = silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j]));
+                    } else {
+                        tmem_ld_wait(v);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int cj = col + j;
-                        const float ws = cj < p.n_out ? __ldg(w_scale_g + cj) : 0.0f;
-                        f[j] = f[j] * x_scale * ws;
+                        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                     }
-                }
-                if constexpr (EPI == 2) {
-                    if (store_ok) {
-                        const size_t off = static_cast<size_t>(drow) * p.ldy + col;
-                        float* d32 = static_cast<float*>(p.y) + off;
-                        const float* c32 = p.c_in + off;
-                        const bool use_c = p.beta != 0.0f;
-                        if ((col + 32 <= p.n_out) && ((reinterpret_cast<uintptr_t>(d32) & 15u) == 0) &&
-                            ((reinterpret_cast<uintptr_t>(c32) & 15u) == 0)) {
+                    if constexpr (SCALE == 1) {
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) {
-                                float4 cv = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if (use_c) cv = __ldg(reinterpret_cast<const float4*>(c32) + q);
-                                float4 o;
-                                o.x = p.alpha * f[q * 4 + 0] + p.beta * cv.x;
-                                o.y = p.alpha * f[q * 4 + 1] + p.beta * cv.y;
-                                o.z = p.alpha * f[q * 4 + 2] + p.beta * cv.z;
-                                o.w = p.alpha * f[q * 4 + 3] + p.beta * cv.w;
-                                reinterpret_cast<float4*>(d32)[q] = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col + j < p.n_out)
-                                    d32[j] = p.alpha * f[j] + (use_c ? p.beta * c32[j] : 0.0f);
+                        for (int j = 0; j < 32; ++j) {
+                            const int cj = col + j;
+                            const float ws = cj < p.n_out ? __ldg(w_scale_g + cj) : 0.0f;
+                            f[j] = f[j] * x_scale * ws;
                         }
                     }
-                } else if (store_ok) {
-                    __nv_bfloat16* dst = y_row + col;
-                    const bool vec = (col + 32 <= p.n_out) && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
-                    if (vec) {
-                        uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint4 o;
-                            o.x = pack_bf16x2(f[q * 8 + 0], f[q * 8 + 1]);
-                            o.y = pack_bf16x2(f[q * 8 + 2], f[q * 8 + 3]);
-                            o.z = pack_bf16x2(f[q * 8 + 4], f[q * 8 + 5]);
-                            o.w = pack_bf16x2(f[q * 8 + 6], f[q * 8 + 7]);
-                            d4[q] = o;
-                        }
+                    if constexpr (EPI == 2) {
+                        if (store_ok)
+                            store_row_chunk_axpby(reinterpret_cast<float*>(my_row),
+                                                  reinterpret_cast<const float*>(my_c), col, p.n_out, f, p.alpha,
+                                                  p.beta);
+                    } else if (!to_peers) {
+                        if (store_ok) store_row_chunk(reinterpret_cast<__nv_bfloat16*>(my_row), col, p.n_out, f);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < p.n_out) dst[j] = __float2bfloat16_rn(f[j]);
+                        for (int q = 0; q < 4; ++q)
+                            stage_put<128>(stage, lane, part * 4 + q,
+                                      make_uint4(pack_bf16x2(f[q * 8 + 0], f[q * 8 + 1]),
+                                                 pack_bf16x2(f[q * 8 + 2], f[q * 8 + 3]),
+                                                 pack_bf16x2(f[q * 8 + 4], f[q * 8 + 5]),
+                                                 pack_bf16x2(f[q * 8 + 6], f[q * 8 + 7])));
+                    }
+                }
+                if constexpr (EPI != 2) {
+                    if (to_peers) {
+                        __syncwarp();
+                        stage_flush<2, 128>(stage, lane,
+                                       my_row != nullptr ? my_row + static_cast<size_t>(scol) * kOutElem : nullptr,
+                                       min(128, (p.n_out - scol) * kOutElem));
+                        __syncwarp();
                     }
                 }
             }
@@ -269,7 +262,7 @@ template <int ELEM_BYTES, int CTAS, int SCALE, int EPI>
 static int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const GGParams& p, int sms,
                           cudaStream_t stream) {
     auto kernel = gg_kernel<ELEM_BYTES, CTAS, SCALE, EPI>;
-    constexpr size_t smem = gg_smem_bytes<CTAS>();
+    constexpr size_t smem = gg_smem_bytes<CTAS, 0, kEpiWarps * kWarpStageBytes>();
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);

@@ -25,17 +25,18 @@ namespace b200moe {
 
 constexpr int kBlkThreads = 384;
 constexpr int kBlkEpiWarps = 8;
+constexpr int kBlkStageBytes = 32 * 64;  // peer-store staging per warp: 32 rows x 64 bytes
 
 template <int CTAS, int EPI>
 __global__ void __launch_bounds__(kBlkThreads, 1)
 gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                     const GGParams p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
-    using Cfg = StageCfg<CTAS>;
+    using Cfg = StageCfg<CTAS, 0>;
     constexpr int kTileRows = kRowsPerCta * CTAS;
 
     extern __shared__ uint8_t smem_raw[];
-    const SmemView sv = carve_smem<CTAS>(smem_raw);
+    const SmemView sv = carve_smem<CTAS, 0>(smem_raw);
     const uint32_t ring_addr = sv.ring_addr;
     SmemTail* st = sv.tail;
     volatile int* abort_flag = &st->abort_flag;
@@ -52,7 +53,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     }
     __syncthreads();
     if (warp == 0) {
-        build_tables_and_barriers<CTAS>(st, p, lane, kTileRows, kBlkEpiWarps * CTAS);
+        build_tables_and_barriers<CTAS, 0>(st, p, lane, kTileRows, kBlkEpiWarps * CTAS);
         if (lane == 0) {
             prefetch_tensormap(&tm_x);
             prefetch_tensormap(&tm_w);
@@ -75,7 +76,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
       if (warp == 0) {
         if (lane == 0)
-            producer_loop<CTAS, EPI == 1>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters, 128,
+            producer_loop<CTAS, 0, EPI == 1>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters, 128,
                                           num_kb);
       } else if (warp == 1) {
         // ================= MMA issuer: one K block per stage, one TMEM buffer per K block
@@ -196,25 +197,63 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             }
             if (!ok) break;
 
-            // ---- store: the thread's row, its (up to) 128 output columns
+            // ---- store: the thread's row, its (up to) 128 output columns, 64 at a time through
+            // the warp's staging buffer so that whole 128-byte runs of a row go out together
             RowDest rd;
             const bool store_ok = resolve_row_dest(p, row, row_ok, &rd);
-            if (store_ok) {
-                __nv_bfloat16* const y_row =
-                    rd.base + static_cast<size_t>(rd.drow) * p.ldy + static_cast<size_t>(tc.g) * p.y_col_group_stride;
-                if constexpr (EPI == 1) {
-                    const int col = tc.n_idx * 128 + half * 64;  // 64 output columns: silu(gate) * up
+            char* const my_row = store_ok ? reinterpret_cast<char*>(rd.base) +
+                                                (static_cast<size_t>(rd.drow) * p.ldy +
+                                                 static_cast<size_t>(tc.g) * p.y_col_group_stride) * 2
+                                          : nullptr;
+            uint4* const stage = sv.warp_stage + ew * (kBlkStageBytes / 16);
+            constexpr int kSlabs = EPI == 1 ? 1 : 2;
+            const int col_first = EPI == 1 ? tc.n_idx * 128 + half * 64 : tc.n_idx * kTileN + half * 128;
+            const bool to_peers = p.row_tags != nullptr;  // kernel-uniform
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        float f[32];
+            for (int sl = 0; sl < kSlabs; ++sl) {
+                const int scol = col_first + sl * 64;
+                if (scol >= p.n_out) continue;  // warp-uniform
+                if (!to_peers) {
+                    if (store_ok) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = silu_mul(acc[c * 32 + j], acc[64 + c * 32 + j]);
-                        store_row_chunk(y_row, col + c * 32, p.n_out, f);
+                        for (int c = 0; c < 2; ++c) {
+                            float f[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if constexpr (EPI == 1)
+                                    f[j] = silu_mul(acc[c * 32 + j], acc[64 + c * 32 + j]);
+                                else
+                                    f[j] = acc[sl * 64 + c * 32 + j];
+                            }
+                            store_row_chunk(reinterpret_cast<__nv_bfloat16*>(my_row), scol + c * 32, p.n_out, f);
+                        }
                     }
                 } else {
-                    const int col = tc.n_idx * kTileN + half * 128;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) store_row_chunk(y_row, col + c * 32, p.n_out, &acc[c * 32]);
+                    for (int hrun = 0; hrun < 2; ++hrun) {  // two 64-byte runs (32 columns each)
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            float f[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int jj = hrun * 32 + q * 8 + j;
+                                if constexpr (EPI == 1)
+                                    f[j] = silu_mul(acc[jj], acc[64 + jj]);
+                                else
+                                    f[j] = acc[sl * 64 + jj];
+                            }
+                            stage_put<64>(stage, lane, q,
+                                          make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                                     pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7])));
+                        }
+                        __syncwarp();
+                        const int rcol = scol + hrun * 32;
+                        if (rcol < p.n_out)
+                            stage_flush<2, 64>(stage, lane,
+                                               my_row != nullptr ? my_row + static_cast<size_t>(rcol) * 2 : nullptr,
+                                               min(64, (p.n_out - rcol) * 2));
+                        __syncwarp();
+                    }
                 }
             }
         }
@@ -240,7 +279,7 @@ template <int CTAS, int EPI>
 static int launch_block_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const GGParams& p, int sms,
                                 cudaStream_t stream) {
     auto kernel = gg_fp8_block_kernel<CTAS, EPI>;
-    constexpr size_t smem = gg_smem_bytes<CTAS>();
+    constexpr size_t smem = gg_smem_bytes<CTAS, 0, kBlkEpiWarps * kBlkStageBytes>();
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);

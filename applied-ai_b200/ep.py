@@ -217,6 +217,8 @@ class ExpertParallelMoE:
         self._remap = None
         self.exchange = exchange
         self.peer = None
+        self.profile = False     # when True, forward() records CUDA-event timings of its phases
+        self.timings = []        # [(phase, milliseconds)] of the last profiled forward
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
         if exchange == "peer" and self.P > 1:
@@ -245,7 +247,15 @@ class ExpertParallelMoE:
         lib = _lib.load()
         stream = torch.cuda.current_stream().cuda_stream
         word = gg._status_word(dev)
+        marks = []
 
+        def mark(name):
+            if self.profile:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         m_glob, offsets, perm, inv_perm = ops.route(topk_ids, self.E)
         counts = torch.empty((P, self.E), dtype=torch.int32, device=dev)
         dist.all_gather_into_tensor(counts, m_glob, group=self.group)
@@ -253,7 +263,9 @@ class ExpertParallelMoE:
         m_loc = torch.empty(self.e_local, dtype=torch.int32, device=dev)
         _lib.check(lib.b200moe_ep_plan(counts.data_ptr(), P, self.E, pb.me, pb.cap, dst_base.data_ptr(),
                                        m_loc.data_ptr(), word.data_ptr(), stream), "ep_plan")
+        mark("route+plan")
         parts = ops.dispatch_payloads(hidden)
+        mark("quantise tokens")
         p1 = parts[1] if len(parts) > 1 else None
         rc = lib.b200moe_ep_push(parts[0].data_ptr(), pb.part_row_bytes[0], 0 if p1 is None else p1.data_ptr(),
                                  pb.part_row_bytes[1] if p1 is not None else 0, perm.data_ptr(), k,
@@ -261,13 +273,22 @@ class ExpertParallelMoE:
                                  pb.tables[0].data_ptr(), pb.tables[1].data_ptr() if p1 is not None else 0,
                                  pb.tables[len(parts)].data_ptr(), stream)
         _lib.check(rc, "ep_push")
+        mark("push")
         dist.all_reduce(pb.sync, group=self.group)          # every rank's rows have landed everywhere
+        mark("barrier 1")
         rows = []
         for buf, nbytes, part in zip(pb.parts, pb.part_row_bytes, parts):
             rows.append(buf.view(part.dtype).view(pb.cap, nbytes // part.element_size()))
         ops.expert_ffn(rows, m_loc, peer=(pb.tags, pb.tables[len(parts) + 1], P, pb.home_rows))
+        mark("experts (down GEMM stores home)")
         dist.all_reduce(pb.sync, group=self.group)          # every result row is home
-        return ops.combine(pb.y_home[:R], inv_perm, topk_weights, T, k)
+        mark("barrier 2")
+        out = ops.combine(pb.y_home[:R], inv_perm, topk_weights, T, k)
+        mark("combine")
+        if self.profile:
+            torch.cuda.synchronize()
+            self.timings = [(marks[i][0], marks[i - 1][1].elapsed_time(marks[i][1])) for i in range(1, len(marks))]
+        return out
 
     def _key_table(self, device):
         """Sort key of every global expert: (wave, destination rank, expert inside the wave), so

@@ -495,6 +495,13 @@ def run_layer(args):
     status = int(B.groupgemm._status_word(dev).item())
     assert status == 0, f"device status {status}"
     assert bool(torch.isfinite(out.float()).all())
+    phase_ms = None
+    if layer.peer is not None:
+        step()
+        layer.profile = True
+        step()
+        layer.profile = False
+        phase_ms = {name: round(ms, 3) for name, ms in layer.timings}
 
     if world == 1 and rank == 0:
         # parity guard: a few tokens through the host restatement of the same layer
@@ -611,6 +618,7 @@ def run_layer(args):
                     "d2h_bytes_per_step": t_loc * H * 2, "ms_per_step": ms_e2e,
                     "note": "per-rank token shard from pinned host memory, output back to host; weights resident"},
             "gpu_launches": args.steps * (16 if mode != "bf16" else 12),
+            "phase_ms_rank0": phase_ms,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -127,8 +127,8 @@ int b200moe_grouped_gemm_ex(const b200moe_gemm_desc* desc, b200moe_stream_t stre
  * expert.  Order on the owner: expert, then source rank, then source order.  Sets status
  * B200MOE_SCAPACITY if some rank would receive more than capacity_rows rows.
  * b200moe_ep_push: for every routed row p (sorted by global expert: perm, offsets from
- * b200moe_route) copy its token's bytes (part0 and optionally part1, row sizes multiples of
- * 16) into the owner's buffers peer_part0[d] / peer_part1[d] at row dst_base[e] + i and
+ * b200moe_route) copy its token's bytes (part0, row size a multiple of 16, and optionally
+ * part1, row size a multiple of 4) into the owner's buffers peer_part0[d] / peer_part1[d] at row dst_base[e] + i and
  * write peer_tags[d][row] = (my_rank << 32) | p.  Rows past capacity_rows are dropped.
  * The peer_* arrays are DEVICE arrays of P pointers into buffers of capacity_rows rows on
  * each rank, mapped into this process (CUDA IPC); call b200moe_enable_peer_access for each
