@@ -155,7 +155,8 @@ class PeerBuffers:
                 _lib.check(lib.b200moe_ipc_open(h, ctypes.byref(base)), "ipc_open")
                 self._opened.append(base.value)
                 torch.cuda.synchronize()
-                _lib.check(lib.b200moe_peer_probe(base.value + off, scratch.data_ptr()), "peer_probe")
+                # every rank probes its own word of the peer's arena, so concurrent probes cannot collide
+                _lib.check(lib.b200moe_peer_probe(base.value + off + 8 * self.me, scratch.data_ptr()), "peer_probe")
                 bases.append(base.value + off)
         # device tables of base addresses, one per buffer kind, indexed by rank
         self.tables = [torch.tensor([bases[r] + o for r in range(self.P)], dtype=torch.int64, device=device)
