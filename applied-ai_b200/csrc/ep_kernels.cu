@@ -65,7 +65,11 @@ ep_push_kernel(const uint8_t* __restrict__ part0, long long bytes0, const uint8_
                long long* const* __restrict__ peer_tag) {
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
-    for (int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < R; p += warps_total) {
+    // Every rank starts its walk over the (destination-sorted) rows at a different place, so
+    // that at any moment the ranks write to different destinations instead of all to the same.
+    const int rot = static_cast<int>(static_cast<long long>(me) * R / (E / e_local));
+    for (int p0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p0 < R; p0 += warps_total) {
+        const int p = p0 + rot < R ? p0 + rot : p0 + rot - R;
         int lo = 0, hi = E - 1;  // global expert of sorted position p: last ge with offsets[ge] <= p
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
