@@ -78,7 +78,7 @@ class GemmDesc(ctypes.Structure):
                 ("M", _c_int), ("N", _c_int), ("K", _c_int), ("G", _c_int), ("ldy", _c_i64),
                 ("y_col_group_stride", _c_i64), ("kind", _c_int), ("epilogue", _c_int), ("cta_group", _c_int),
                 ("y_rows", _c_int), ("y_row_map", _c_vp), ("y_row_tags", _c_vp), ("y_peer_bases", _c_vp),
-                ("n_peers", _c_int), ("status", _c_vp)]
+                ("n_peers", _c_int), ("status", _c_vp), ("y_scale_out", _c_vp)]
 
 
 class B200MoeError(RuntimeError):

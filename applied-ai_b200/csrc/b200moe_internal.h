@@ -38,6 +38,7 @@ struct GGParams {
     const long long* row_tags;     // optional: row r goes to peer_y[tag >> 32] at row (tag & 0xffffffff)
     void* const* peer_y;           //   bases of y on every rank (device array, n_peers entries)
     int n_peers;
+    float* y_scale_out;            // EPI 3: fp32 scales of the e4m3 output, [M, n_out/128]
     const float* c_in;             // fp32 epilogue: the C operand of alpha*acc + beta*C (same layout as y)
     float alpha, beta;
     uint32_t idesc;                // tcgen05 instruction descriptor (operand formats, tile shape)
@@ -61,6 +62,7 @@ struct GGLaunch {
     const long long* row_tags;
     void* const* peer_y;
     int n_peers;
+    float* y_scale_out;
     const float* c_in;
     float alpha, beta;
     int is_f16;      // 2-byte operands are IEEE half instead of bf16
@@ -70,7 +72,7 @@ struct GGLaunch {
     int M, N, K, G;
     int elem_bytes;  // 2 bf16/f16, 1 e4m3
     int scale_mode;  // 0 none, 1 row-wise
-    int epilogue;    // 0 plain, 1 SwiGLU, 2 fp32 out = alpha*acc + beta*C
+    int epilogue;    // 0 plain, 1 SwiGLU, 2 fp32 out = alpha*acc + beta*C, 3 SwiGLU -> e4m3 + 1x128 scales
     int cta_group;   // 0 auto, 1 or 2
     cudaStream_t stream;
 };

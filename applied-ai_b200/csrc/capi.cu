@@ -134,7 +134,10 @@ int b200moe_grouped_gemm_ex(const b200moe_gemm_desc* d, b200moe_stream_t stream)
     a.stream = static_cast<cudaStream_t>(stream);
     if (d->ldy <= 0 || d->y_col_group_stride < 0 || d->m_sizes == nullptr) return kErrBadArgument;
     if ((d->y_row_map != nullptr || d->y_row_tags != nullptr) && d->y_rows <= 0) return kErrBadArgument;
-    if (d->epilogue != B200MOE_EPI_NONE && d->epilogue != B200MOE_EPI_SWIGLU) return kErrBadArgument;
+    if (d->epilogue != B200MOE_EPI_NONE && d->epilogue != B200MOE_EPI_SWIGLU &&
+        !(d->epilogue == B200MOE_EPI_SWIGLU_FP8 && d->kind == B200MOE_KIND_FP8_BLOCKWISE))
+        return kErrBadArgument;
+    a.y_scale_out = d->y_scale_out;
     switch (d->kind) {
         case B200MOE_KIND_BF16:
             a.elem_bytes = 2;

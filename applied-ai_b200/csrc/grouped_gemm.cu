@@ -338,6 +338,7 @@ int grouped_gemm_launch(const GGLaunch& a) {
     // would be padding, so small groups use the single-CTA 128-row tile.
     const int ctas = a.cta_group == 1 ? 1 : a.cta_group == 2 ? 2 : (a.M / a.G >= 256 ? 2 : 1);
     const bool fp8 = a.elem_bytes == 1;
+    p.y_scale_out = nullptr;
     p.c_in = a.c_in;
     p.alpha = a.alpha;
     p.beta = a.beta;

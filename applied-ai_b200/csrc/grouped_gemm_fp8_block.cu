@@ -19,6 +19,8 @@
 // setmaxnreg moves registers from the first warpgroup to the two epilogue warpgroups so
 // those accumulators stay in registers.  Tile shapes, scheduler and the CTA-pair mode are
 // those of the bf16 kernel (grouped_gemm.cu).
+#include <cuda_fp8.h>
+
 #include "gg_common.cuh"
 
 namespace b200moe {
@@ -27,6 +29,9 @@ constexpr int kBlkThreads = 384;
 constexpr int kBlkEpiWarps = 8;
 constexpr int kBlkStageBytes = 32 * 64;  // peer-store staging per warp: 32 rows x 64 bytes
 
+// EPI: 0 plain, 1 SwiGLU -> bf16, 3 SwiGLU -> e4m3 with one fp32 scale per row and 128 columns
+//      (the 1x128 quantiser of float8_groupwise_quant.py:36-46 applied to the fp32 values in
+//      registers, so the intermediate never exists in bf16).
 template <int CTAS, int EPI>
 __global__ void __launch_bounds__(kBlkThreads, 1)
 gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
@@ -34,6 +39,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
     using Cfg = StageCfg<CTAS, 0>;
     constexpr int kTileRows = kRowsPerCta * CTAS;
+    constexpr bool kSwiglu = EPI == 1 || EPI == 3;
 
     extern __shared__ uint8_t smem_raw[];
     const SmemView sv = carve_smem<CTAS, 0>(smem_raw);
@@ -51,6 +57,11 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         st->abort_flag = 0;
         st->invalid = 0;
     }
+    // Mailbox through which the two warps that share 32 rows exchange their half-row maxima
+    // (EPI 3): amax[slot][half][row] and a sequence word per (slot, half, lane quarter).
+    float* const mail_amax = reinterpret_cast<float*>(sv.warp_stage);
+    volatile int* const mail_seq = reinterpret_cast<volatile int*>(mail_amax + 2 * 2 * 128);
+    if (threadIdx.x < 16) mail_seq[threadIdx.x] = 0;
     __syncthreads();
     if (warp == 0) {
         build_tables_and_barriers<CTAS, 0>(st, p, lane, kTileRows, kBlkEpiWarps * CTAS);
@@ -76,7 +87,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
       if (warp == 0) {
         if (lane == 0)
-            producer_loop<CTAS, 0, EPI == 1>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters, 128,
+            producer_loop<CTAS, 0, kSwiglu>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters, 128,
                                           num_kb);
       } else if (warp == 1) {
         // ================= MMA issuer: one K block per stage, one TMEM buffer per K block
@@ -127,7 +138,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             CTAS == 1 ? smem_u32(&st->acc_empty[0]) : mapa_shared(smem_u32(&st->acc_empty[0]), 0);
         const int kblocks = num_kb;                    // scales per row of x
         const int nblocks = (p.N + 127) / 128;         // scale blocks per expert along N
-        int g = 0, buf = 0;
+        int g = 0, buf = 0, tiles_done = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
@@ -139,10 +150,10 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             //   plain : columns half*128 + [0,128)            -> scale block 2*n_idx + half
             //   SwiGLU: gate columns half*64 + [0,64) (block n_idx) and the matching up
             //           columns 128 + half*64 + [0,64) (block I/128 + n_idx)
-            const int col_a = EPI == 1 ? half * 64 : half * 128;
-            const int col_b = EPI == 1 ? 128 + half * 64 : half * 128 + 64;
-            const int blk_a = EPI == 1 ? tc.n_idx : 2 * tc.n_idx + half;
-            const int blk_b = EPI == 1 ? p.n_out / 128 + tc.n_idx : blk_a;
+            const int col_a = kSwiglu ? half * 64 : half * 128;
+            const int col_b = kSwiglu ? 128 + half * 64 : half * 128 + 64;
+            const int blk_a = kSwiglu ? tc.n_idx : 2 * tc.n_idx + half;
+            const int blk_b = kSwiglu ? p.n_out / 128 + tc.n_idx : blk_a;
             const float* ws_a = p.w_scale + (static_cast<size_t>(tc.g) * nblocks + min(blk_a, nblocks - 1)) * kblocks;
             const float* ws_b = p.w_scale + (static_cast<size_t>(tc.g) * nblocks + min(blk_b, nblocks - 1)) * kblocks;
 
@@ -197,6 +208,71 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             }
             if (!ok) break;
 
+            if constexpr (EPI == 3) {
+                // ---- SwiGLU, then 1x128 quantisation of the 128 output columns this tile owns for
+                // the row; this thread holds 64 of them, the warp with the other half holds the rest.
+                ++tiles_done;
+                float f[64];
+                float amax = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    f[j] = silu_mul(acc[j], acc[64 + j]);
+                    amax = fmaxf(amax, fabsf(f[j]));
+                }
+                const int slot = tiles_done & 1;
+                const int rix = quarter * 32 + lane;
+                mail_amax[(slot * 2 + half) * 128 + rix] = amax;
+                __threadfence_block();
+                __syncwarp();
+                if (lane == 0) mail_seq[(slot * 2 + half) * 4 + quarter] = tiles_done;
+                // bounded wait for the partner warp's half
+                int seen = 0;
+                if (lane == 0) {
+                    const uint64_t t0 = globaltimer_ns();
+                    uint32_t spins = 0;
+                    seen = 1;
+                    while (mail_seq[(slot * 2 + (half ^ 1)) * 4 + quarter] != tiles_done) {
+                        if (((++spins) & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs)) {
+                            *abort_flag = 1;
+                            seen = 0;
+                            break;
+                        }
+                    }
+                }
+                seen = __shfl_sync(0xffffffffu, seen, 0);
+                if (!seen) {
+                    if (lane == 0) report(p.status, kStatusTimeoutEpilogue);
+                    ok = false;
+                    break;
+                }
+                __threadfence_block();
+                amax = fmaxf(amax, mail_amax[(slot * 2 + (half ^ 1)) * 128 + rix]);
+                const float scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+                const float inv_scale = __fdiv_rn(1.0f, scale);  // one division per row; values use a multiply
+                const int col = tc.n_idx * 128 + half * 64;
+                if (row_ok && col < p.n_out) {
+                    uint8_t* q_row = static_cast<uint8_t*>(p.y) + static_cast<size_t>(row) * p.ldy + col;
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t packed = 0;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float v = f[c4 * 16 + i * 4 + j] * inv_scale;
+                                v = fminf(fmaxf(v, -448.0f), 448.0f);
+                                packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3))
+                                          << (8 * j);
+                            }
+                            w[i] = packed;
+                        }
+                        *reinterpret_cast<uint4*>(q_row + c4 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    if (half == 0) p.y_scale_out[static_cast<size_t>(row) * (p.n_out / 128) + tc.n_idx] = scale;
+                }
+                continue;
+            }
             // ---- store: the thread's row, its (up to) 128 output columns, 64 at a time through
             // the warp's staging buffer so that whole 128-byte runs of a row go out together
             RowDest rd;
@@ -310,9 +386,13 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     if (a.G > kMaxGroups) return kErrTooManyGroups;
     if (a.K % 128 != 0) return kErrAlignment;  // whole scale blocks along K
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.w) & 15u)) return kErrAlignment;
-    if (a.epilogue != 0 && a.epilogue != 1) return kErrBadArgument;
+    if (a.epilogue != 0 && a.epilogue != 1 && a.epilogue != 3) return kErrBadArgument;
+    if (a.epilogue == 3 && (a.y_scale_out == nullptr || a.row_map != nullptr || a.row_tags != nullptr ||
+                            a.y_col_group_stride != 0 || (a.ldy & 15) != 0 ||
+                            (reinterpret_cast<uintptr_t>(a.y) & 15u) != 0))
+        return kErrBadArgument;
     if (a.row_tags != nullptr && (a.peer_y == nullptr || a.n_peers <= 0 || a.y_rows <= 0)) return kErrBadArgument;
-    if (a.epilogue == 1 && (a.N % 256 != 0)) return kErrBadArgument;  // gate and up halves in whole scale blocks
+    if (a.epilogue != 0 && (a.N % 256 != 0)) return kErrBadArgument;  // gate and up halves in whole scale blocks
     if (a.M == 0) return 0;
 
     DeviceInfo di;
@@ -339,8 +419,9 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.G = a.G;
     p.ldy = a.ldy;
     p.y_col_group_stride = a.y_col_group_stride;
-    p.n_out = a.epilogue == 1 ? a.N / 2 : a.N;
-    p.n_tiles = a.epilogue == 1 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;
+    p.n_out = a.epilogue != 0 ? a.N / 2 : a.N;
+    p.n_tiles = a.epilogue != 0 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;
+    p.y_scale_out = a.y_scale_out;
 
     const int ctas = a.cta_group == 1 ? 1 : a.cta_group == 2 ? 2 : (a.M / a.G >= 256 ? 2 : 1);
     p.c_in = nullptr;
@@ -350,6 +431,9 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     if (a.epilogue == 0)
         return ctas == 1 ? launch_block_variant<1, 0>(tm_x, tm_w, p, di.sms, a.stream)
                          : launch_block_variant<2, 0>(tm_x, tm_w, p, di.sms, a.stream);
+    if (a.epilogue == 3)
+        return ctas == 1 ? launch_block_variant<1, 3>(tm_x, tm_w, p, di.sms, a.stream)
+                         : launch_block_variant<2, 3>(tm_x, tm_w, p, di.sms, a.stream);
     return ctas == 1 ? launch_block_variant<1, 1>(tm_x, tm_w, p, di.sms, a.stream)
                      : launch_block_variant<2, 1>(tm_x, tm_w, p, di.sms, a.stream);
 }

@@ -28,11 +28,14 @@ import torch.distributed as dist
 class CudaOps:
     """The layer's compute steps on the GPU.  mode: "bf16" or "fp8_blockwise"."""
 
-    def __init__(self, w1, w2, mode="bf16", cta_group=0):
+    def __init__(self, w1, w2, mode="bf16", cta_group=0, fuse_requant=False):
+        """fuse_requant (fp8_blockwise): quantise the SwiGLU output inside the gate+up GEMM's epilogue
+        instead of with a separate 1x128 quantiser pass."""
         from . import groupgemm, moe, quant
         self._gg, self._moe, self._quant = groupgemm, moe, quant
         self.mode = mode
         self.cta_group = cta_group
+        self.fuse_requant = bool(fuse_requant)
         if mode == "bf16":
             self.w1, self.w2 = w1.contiguous(), w2.contiguous()
         elif mode == "fp8_blockwise":
@@ -80,9 +83,7 @@ class CudaOps:
                 return gg.grouped_gemm_ex(gg.KIND_BF16, h, self.w2, m_sizes, cta_group=self.cta_group,
                                           out_row_tags=tags, peer_bases=bases, n_peers=n_peers, out_rows=y_rows)
             xq, xs = rows[0].view(torch.float8_e4m3fn), rows[1]
-            h = gg.grouped_gemm_fp8_blockwise(xq, self.w1, m_sizes, xs, self.w1_scale, epilogue="swiglu",
-                                              check=False, cta_group=self.cta_group)
-            hq, hs = self._quant.float8_groupwise_quantize(h)
+            hq, hs = self._gate_up_fp8(xq, xs, self.w1, self.w1_scale, m_sizes)
             return gg.grouped_gemm_ex(gg.KIND_FP8_BLOCKWISE, hq, self.w2, m_sizes, x_scale=hs, w_scale=self.w2_scale,
                                       cta_group=self.cta_group, out_row_tags=tags, peer_bases=bases,
                                       n_peers=n_peers, out_rows=y_rows)
@@ -92,11 +93,19 @@ class CudaOps:
             return gg.grouped_gemm(h, self.w2[lo:hi], m_sizes, check=False, cta_group=self.cta_group,
                                    out_row_map=out_row_map)
         xq, xs = rows[0].view(torch.float8_e4m3fn), rows[1]
-        h = gg.grouped_gemm_fp8_blockwise(xq, self.w1[lo:hi], m_sizes, xs, self.w1_scale[lo:hi], epilogue="swiglu",
-                                          check=False, cta_group=self.cta_group)
-        hq, hs = self._quant.float8_groupwise_quantize(h)
+        hq, hs = self._gate_up_fp8(xq, xs, self.w1[lo:hi], self.w1_scale[lo:hi], m_sizes)
         return gg.grouped_gemm_fp8_blockwise(hq, self.w2[lo:hi], m_sizes, hs, self.w2_scale[lo:hi], check=False,
                                              cta_group=self.cta_group, out_row_map=out_row_map)
+
+    def _gate_up_fp8(self, xq, xs, w1, w1_scale, m_sizes):
+        """gate+up GEMM with SwiGLU -> (e4m3 rows, 1x128 scales) for the down GEMM."""
+        gg = self._gg
+        if self.fuse_requant:
+            return gg.grouped_gemm_ex(gg.KIND_FP8_BLOCKWISE, xq, w1, m_sizes, x_scale=xs, w_scale=w1_scale,
+                                      epilogue="swiglu_fp8", cta_group=self.cta_group)
+        h = gg.grouped_gemm_fp8_blockwise(xq, w1, m_sizes, xs, w1_scale, epilogue="swiglu", check=False,
+                                          cta_group=self.cta_group)
+        return self._quant.float8_groupwise_quantize(h)
 
     def combine(self, y, inv_perm, topk_weights, num_tokens, top_k):
         return self._moe.combine_topk(y, inv_perm, topk_weights, num_tokens, top_k)

@@ -210,12 +210,20 @@ def grouped_gemm_ex(kind, x, w, m_sizes, *, x_scale=None, w_scale=None, epilogue
     entry points do, result rows can be sent to (rank, row) destinations: out_row_tags int64 [M]
     = (rank << 32) | row and peer_bases = int64 device tensor of n_peers base addresses of bf16
     buffers with out_rows rows each (this rank's own buffer included).  Returns y, or None when
-    rows go to peer buffers."""
+    rows go to peer buffers.  epilogue="swiglu_fp8" (block-wise kind): returns (e4m3 [M, N/2],
+    fp32 scales [M, N/256]) — silu(gate)*up quantised 1x128 inside the GEMM."""
     import ctypes
     m_sizes, G, M, N, K = _prepare(x, w, m_sizes, torch.bfloat16 if kind == KIND_BF16 else torch.float8_e4m3fn)
-    epi = {"none": 0, "swiglu": 1}[epilogue]
-    n_out = N // 2 if epi == 1 else N
+    epi = {"none": 0, "swiglu": 1, "swiglu_fp8": 3}[epilogue]
+    n_out = N // 2 if epi != 0 else N
     d = _lib.GemmDesc()
+    y_scale = None
+    if epi == 3:
+        _require(kind == KIND_FP8_BLOCKWISE and N % 256 == 0 and out_row_map is None and out_row_tags is None,
+                 "the quantising SwiGLU epilogue needs the block-wise kind, N % 256 == 0 and plain row placement")
+        y = torch.empty((M, n_out), device=x.device, dtype=torch.float8_e4m3fn)
+        y_scale = torch.empty((M, n_out // 128), device=x.device, dtype=torch.float32)
+        d.y_scale_out = y_scale.data_ptr()
     d.x, d.w, d.m_sizes = x.data_ptr(), w.data_ptr(), m_sizes.data_ptr()
     d.x_scale = 0 if x_scale is None else x_scale.data_ptr()
     d.w_scale = 0 if w_scale is None else w_scale.data_ptr()
@@ -244,4 +252,6 @@ def grouped_gemm_ex(kind, x, w, m_sizes, *, x_scale=None, w_scale=None, epilogue
         _lib.check(rc, "grouped_gemm_ex")
         if check:
             raise_on_status(word, "grouped_gemm_ex")
+    if epi == 3:
+        return y, y_scale
     return None if out_row_tags is not None else y

@@ -475,7 +475,7 @@ def run_layer(args):
     for e in range(e_loc):
         w1[e] = (torch.randn(2 * I, H, generator=gd, device=dev) * H ** -0.5).to(torch.bfloat16)
         w2[e] = (torch.randn(H, I, generator=gd, device=dev) * I ** -0.5).to(torch.bfloat16)
-    ops = CudaOps(w1, w2, mode=mode, cta_group=args.cta_group)
+    ops = CudaOps(w1, w2, mode=mode, cta_group=args.cta_group, fuse_requant=args.fuse_requant)
     if mode != "bf16":
         del w1, w2
     layer = ExpertParallelMoE(ops, E, waves=args.waves, exchange=args.exchange, max_tokens=t_loc, top_k=k,
@@ -522,7 +522,7 @@ def run_layer(args):
                     one = torch.tensor([1], dtype=torch.int32)
                     h1 = O.silu_and_mul_ref(O.grouped_gemm_fp8_blockwise_ref(
                         xq, ops.w1[e].cpu()[None], one, xs, ops.w1_scale[e].cpu()[None]))
-                    hq, hs = O.quant_1x128_ref(h1.to(torch.bfloat16))
+                    hq, hs = O.quant_1x128_ref(h1 if ops.fuse_requant else h1.to(torch.bfloat16))
                     ye = O.grouped_gemm_fp8_blockwise_ref(hq, ops.w2[e].cpu()[None], one, hs,
                                                           ops.w2_scale[e].cpu()[None])
                 ref[i] += float(w_p[i, j]) * ye.to(torch.bfloat16).float()[0]
@@ -704,6 +704,8 @@ def main():
                     help="expert-parallel layers: chunks of local experts whose exchange overlaps compute")
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="expert-parallel layers: NCCL all-to-all, or remote stores into peer memory")
+    ap.add_argument("--fuse-requant", action="store_true", dest="fuse_requant",
+                    help="FP8 layers: quantise the SwiGLU output inside the gate+up GEMM")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture, echoed into the roofline object")
     args = ap.parse_args()

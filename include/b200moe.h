@@ -45,6 +45,8 @@ typedef void* b200moe_stream_t;
 /* flags of the grouped GEMM entry points */
 #define B200MOE_EPI_NONE 0
 #define B200MOE_EPI_SWIGLU 1  /* w[g] = [gate rows 0..N/2) ; up rows N/2..N); y gets N/2 columns: silu(gate)*up */
+#define B200MOE_EPI_SWIGLU_FP8 3 /* block-wise FP8 kind via b200moe_grouped_gemm_ex only: silu(gate)*up quantised in the
+                                   epilogue to e4m3 [M, N/2] (y, row pitch ldy BYTES) + fp32 scales [M, N/256] (y_scale_out) */
 #define B200MOE_CTA_AUTO 0    /* 1 = one CTA per 128x256 tile, 2 = a CTA pair per 256x256 tile */
 
 int b200moe_version(void);
@@ -117,6 +119,7 @@ typedef struct b200moe_gemm_desc {
     void* const* y_peer_bases;/* device array of n_peers base pointers */
     int n_peers;
     int32_t* status;
+    float* y_scale_out;       /* B200MOE_EPI_SWIGLU_FP8: scales of the quantised output */
 } b200moe_gemm_desc;
 int b200moe_grouped_gemm_ex(const b200moe_gemm_desc* desc, b200moe_stream_t stream);
 

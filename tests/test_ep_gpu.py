@@ -34,7 +34,7 @@ def test_single_rank_bf16_equals_fused_moe():
 
 def fp8_layer_reference(hidden, ops, tw, ids):
     """The layer on the same quantised operands: 1x128-quantised tokens, block-quantised
-    weights, intermediate rounded to bf16 and quantised 1x128 again before the down GEMM."""
+    weights, intermediate quantised 1x128 again (from fp32) before the down GEMM."""
     E = ops.w1.shape[0]
     xq, xs = O.quant_1x128_ref(hidden)
     T, k = ids.shape
@@ -47,16 +47,17 @@ def fp8_layer_reference(hidden, ops, tw, ids):
                 continue
             m = torch.tensor([rows.numel()], dtype=torch.int32)
             h = O.silu_and_mul_ref(O.grouped_gemm_fp8_blockwise_ref(xq[rows], w1[e][None], m, xs[rows], s1[e][None]))
-            hq, hs = O.quant_1x128_ref(h.to(torch.bfloat16))
+            hq, hs = O.quant_1x128_ref(h.to(torch.bfloat16) if not ops.fuse_requant else h)
             y = O.grouped_gemm_fp8_blockwise_ref(hq, w2[e][None], m, hs, s2[e][None]).to(torch.bfloat16).float()
             out[rows] += tw[rows, j:j + 1].float() * y
     return out
 
 
-def test_single_rank_fp8_blockwise_layer():
+@pytest.mark.parametrize("fuse", [False, True])
+def test_single_rank_fp8_blockwise_layer(fuse):
     hidden, w1, w2, tw, ids = problem(200, 256, 256, 4, 2, 2)
     d = "cuda"
-    ops = CudaOps(w1.to(d), w2.to(d), "fp8_blockwise")
+    ops = CudaOps(w1.to(d), w2.to(d), "fp8_blockwise", fuse_requant=fuse)
     out = ExpertParallelMoE(ops, 4)(hidden.to(d), tw.to(d), ids.to(d))
     ref = fp8_layer_reference(hidden, ops, tw, ids)
     assert O.rel_err(out.cpu().float(), ref) <= FP8_REL_TOL
