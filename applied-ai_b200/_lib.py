@@ -56,6 +56,9 @@ SIGNATURES = {
     "b200moe_peer_probe": [_c_vp, _c_vp],
     "b200moe_sm100_gemm_f16": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, ctypes.c_float, ctypes.c_float,
                                _c_vp],
+    "b200moe_backward_workspace_bytes": [_c_int, _c_int, _c_int, _c_int, ctypes.POINTER(_c_sz)],
+    "b200moe_grouped_gemm_backward": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_i64,
+                                      _c_i64, _c_vp, _c_sz, _c_int, _c_vp, _c_vp],
     "b200moe_selftest_wait_timeout": [ctypes.c_uint64, _c_vp, _c_vp],
     "b200moe_route_workspace_bytes": [_c_int, _c_int, ctypes.POINTER(_c_sz)],
     "b200moe_route": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp],

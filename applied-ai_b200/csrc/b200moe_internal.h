@@ -46,6 +46,7 @@ struct GGParams {
     long long ldy;                 // elements between consecutive rows of y
     long long y_col_group_stride;  // first column of group g's block is g * this (0: all groups share columns)
     int M, N, K, G;
+    long long x_col_group_stride;  // group g's K range in x starts at column g * this (0: shared columns)
     int n_out;    // output columns per group (N, or N/2 with SwiGLU)
     int n_tiles;  // column tiles per group
 };
@@ -69,6 +70,8 @@ struct GGLaunch {
     int y_rows;
     long long ldy;
     long long y_col_group_stride;
+    long long x_ld;                // elements per row of x when it is wider than K (0: K)
+    long long x_col_group_stride;  // see GGParams
     int M, N, K, G;
     int elem_bytes;  // 2 bf16/f16, 1 e4m3
     int scale_mode;  // 0 none, 1 row-wise
@@ -78,6 +81,13 @@ struct GGLaunch {
 };
 
 int grouped_gemm_launch(const GGLaunch& a);
+// Backward pieces (grouped_gemm_dw.cu).
+long long dw_padded_cols(int M, int G);
+int transpose_pad_launch(const void* src, long long ld, long long col_group_stride, int C, const int32_t* m_sizes,
+                         int G, int M, void* out, long long mpad, cudaStream_t stream);
+int transpose_batched_launch(const void* src, void* dst, int B, int R, int C, cudaStream_t stream);
+int grouped_gemm_dw_launch(const void* dyt, const void* xt, const int32_t* m_sizes, void* dw, int M, int N, int K,
+                           int G, long long mpad, int cta_group, int32_t* status, cudaStream_t stream);
 int selftest_wait_launch(uint64_t limit_ns, int32_t* status, cudaStream_t stream);
 // FP8 with 1x128 activation scales [M, K/128] and 128x128 weight scales [G, ceil(N/128), K/128].
 int grouped_gemm_fp8_block_launch(const GGLaunch& a);

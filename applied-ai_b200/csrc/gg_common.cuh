@@ -296,18 +296,19 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
             }
             const uint32_t a_dst = ring_addr + stage * Cfg::kStageBytes;
             const uint32_t b_dst = a_dst + kABytes;
-            const int k0 = kb * elems_per_stage;
+            const int k0 = kb * elems_per_stage;                                     // position along K
+            const int kx = k0 + static_cast<int>(tc.g * p.x_col_group_stride);      // column of x it sits at
             if constexpr (CTAS == 1) {
                 const uint32_t bar = smem_u32(&st->full[stage]);
                 mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
-                tma_load_2d(tm_x, bar, a_dst, k0, row0);
+                tma_load_2d(tm_x, bar, a_dst, kx, row0);
                 tma_load_3d(tm_w, bar, b_dst, k0, nb0, tc.g);
                 tma_load_3d(tm_w, bar, b_dst + kSubBoxBytes, k0, nb1, tc.g);
             } else {
                 // Bytes of both CTAs are counted on the leader's barrier.
                 const uint32_t bar = mapa_shared(smem_u32(&st->full[stage]), 0);
                 if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
-                tma_load_2d_pair(tm_x, bar, a_dst, k0, row0);
+                tma_load_2d_pair(tm_x, bar, a_dst, kx, row0);
                 tma_load_3d_pair(tm_w, bar, b_dst, k0, cta_rank == 0 ? nb0 : nb1, tc.g);
             }
             if (++stage == Cfg::kStages) {

@@ -294,6 +294,7 @@ int grouped_gemm_launch(const GGLaunch& a) {
     if (a.G > kMaxGroups) return kErrTooManyGroups;
     if (a.elem_bytes != 1 && a.elem_bytes != 2) return kErrBadArgument;
     if ((static_cast<long long>(a.K) * a.elem_bytes) % 16 != 0) return kErrAlignment;  // TMA row pitch
+    if (a.x_col_group_stride != 0 && (a.x_col_group_stride * a.elem_bytes) % 16 != 0) return kErrAlignment;
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.w) & 15u)) return kErrAlignment;
     if (a.scale_mode == 1 && (a.x_scale == nullptr || a.w_scale == nullptr)) return kErrBadArgument;
     if (a.epilogue == 2 && (a.elem_bytes != 2 || a.scale_mode != 0 || a.y_col_group_stride != 0 ||
@@ -311,7 +312,10 @@ int grouped_gemm_launch(const GGLaunch& a) {
     if (di.cc_major != 10) return kErrWrongDevice;
 
     CUtensorMap tm_x, tm_w;
-    if (int e = encode_x_map(&tm_x, a.x, a.M, a.K, a.elem_bytes, a.is_f16 != 0)) return e;
+    // x may be wider than K (a group's K range is then a column block of it)
+    const long long x_ld = a.x_ld > 0 ? a.x_ld : a.K;
+    if ((x_ld * a.elem_bytes) % 16 != 0 || x_ld > 0x7fffffffll) return kErrAlignment;
+    if (int e = encode_x_map(&tm_x, a.x, a.M, static_cast<int>(x_ld), a.elem_bytes, a.is_f16 != 0)) return e;
     if (int e = encode_w_map(&tm_w, a.w, a.G, a.N, a.K, a.elem_bytes, a.is_f16 != 0)) return e;
 
     GGParams p;
@@ -330,6 +334,7 @@ int grouped_gemm_launch(const GGLaunch& a) {
     p.K = a.K;
     p.G = a.G;
     p.ldy = a.ldy;
+    p.x_col_group_stride = a.x_col_group_stride;
     p.y_col_group_stride = a.y_col_group_stride;
     p.n_out = a.epilogue == 1 ? a.N / 2 : a.N;
     p.n_tiles = a.epilogue == 1 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;

@@ -115,8 +115,9 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         umma<CTAS, true>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
+                    // One commit serves two waiters: the producer (stage free) and the promotion
+                    // warps (this K block's product is in TMEM) both watch empty[stage].
                     umma_commit<CTAS>(&st->empty[stage]);
-                    umma_commit<CTAS>(&st->acc_full[buf]);
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -138,8 +139,8 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             CTAS == 1 ? smem_u32(&st->acc_empty[0]) : mapa_shared(smem_u32(&st->acc_empty[0]), 0);
         const int kblocks = num_kb;                    // scales per row of x
         const int nblocks = (p.N + 127) / 128;         // scale blocks per expert along N
-        int g = 0, buf = 0, tiles_done = 0;
-        uint32_t acc_phase = 0;
+        int g = 0, buf = 0, tiles_done = 0, stage = 0;
+        uint32_t stage_phase = 0;
         bool ok = true;
         for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
             const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
@@ -172,7 +173,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     wb_next = __ldg(ws_b + kb + 1);
                 }
                 // every lane polls: the flip is seen without a shuffle hop
-                const int got = __all_sync(0xffffffffu, mbar_wait(&st->acc_full[buf], acc_phase, abort_flag) ? 1 : 0);
+                const int got = __all_sync(0xffffffffu, mbar_wait(&st->empty[stage], stage_phase, abort_flag) ? 1 : 0);
                 if (!got) {
                     if (lane == 0) report(p.status, kStatusTimeoutEpilogue);
                     ok = false;
@@ -204,7 +205,10 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     acc[96 + j] = fmaf(__uint_as_float(v1[j]), sb, acc[96 + j]);
                 }
                 buf ^= 1;
-                if (buf == 0) acc_phase ^= 1u;
+                if (++stage == Cfg::kStages) {
+                    stage = 0;
+                    stage_phase ^= 1u;
+                }
             }
             if (!ok) break;
 
@@ -418,6 +422,7 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.K = a.K;
     p.G = a.G;
     p.ldy = a.ldy;
+    p.x_col_group_stride = a.x_col_group_stride;
     p.y_col_group_stride = a.y_col_group_stride;
     p.n_out = a.epilogue != 0 ? a.N / 2 : a.N;
     p.n_tiles = a.epilogue != 0 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;

@@ -164,6 +164,21 @@ int b200moe_peer_probe(void* peer_ptr, void* local_scratch8);
 int b200moe_sm100_gemm_f16(const void* A, const void* B, const void* C, void* D, int M, int N, int K, float alpha,
                            float beta, b200moe_stream_t stream);
 
+/* Backward of the grouped GEMM:
+ *   grad_x[rows of g] = grad_y[rows of g, block g] @ w[g]            [M, K] bf16
+ *   grad_w[g]         = grad_y[rows of g, block g]^T @ x[rows of g]  [G, N, K] bf16 (zeros for empty groups)
+ * grad_y is [M, N*G] (block layout: grad_y_ld = N*G, grad_y_col_group_stride = N) or [M, N]
+ * (grad_y_ld = N, stride 0), bf16.  Rows of grad_x past sum(m_sizes) are not written.
+ * Replaces grouped_gemm_backward(grad_output, x, w, m_sizes)
+ *   kernels/MoE/group_GEMM/triton/tgroup_gemm_backwards.py:382 (per-group definition:
+ *   testing/pytorch_reference_backwards.py:165-197).  `workspace` holds transposed copies
+ * (b200moe_backward_workspace_bytes). */
+int b200moe_backward_workspace_bytes(int M, int N, int K, int G, size_t* bytes);
+int b200moe_grouped_gemm_backward(const void* grad_y, const void* x, const void* w, const int32_t* m_sizes,
+                                  void* grad_x, void* grad_w, int M, int N, int K, int G, int64_t grad_y_ld,
+                                  int64_t grad_y_col_group_stride, void* workspace, size_t workspace_bytes,
+                                  int cta_group, int32_t* status, b200moe_stream_t stream);
+
 /* Failure-path self-test: launches one small kernel whose only wait can never be
  * satisfied and whose limit is limit_ns (1 .. 2e9).  After the limit the kernel stops
  * polling, writes B200MOE_SSELFTEST to *status and returns; nothing faults and the

@@ -156,6 +156,30 @@ def quant_1x128_ref(x, block=128):
     return q.reshape(x.shape), scale
 
 
+def grouped_gemm_backward_ref(grad_output, x, w, m_sizes):
+    """(grad_x, grad_w) of the grouped GEMM, group by group in fp32
+    (kernels/MoE/group_GEMM/triton/testing/pytorch_reference_backwards.py:165-197):
+    grad_x[rows_g] = dY[rows_g, block g] @ w[g];  grad_w[g] = dY[rows_g, block g].T @ x[rows_g].
+    grad_output is [M, N*G] (block layout) or [M, N]; zeros where nothing is defined."""
+    G = m_sizes.numel()
+    M, K = x.shape
+    w3 = w.reshape(G, -1, K).float()
+    N = w3.shape[1]
+    dy, xf = grad_output.float(), x.float()
+    blocked = dy.shape[1] == N * G and G > 1
+    grad_x = torch.zeros(M, K)
+    grad_w = torch.zeros(G, N, K)
+    sizes, starts = _offsets(m_sizes)
+    for g in range(G):
+        a, b = starts[g], starts[g] + sizes[g]
+        if sizes[g] == 0:
+            continue
+        blk = dy[a:b, g * N:(g + 1) * N] if blocked else dy[a:b]
+        grad_x[a:b] = blk @ w3[g]
+        grad_w[g] = blk.T @ xf[a:b]
+    return grad_x, grad_w.reshape(w.shape)
+
+
 def dense_gemm_ref(A, B, C, alpha=1.0, beta=0.0):
     """alpha * A @ B.T + beta * C in fp32 — what the reference's Blackwell driver compares
     against with torch.addmm (kernels/blackwell/cute_gemm_02_tma/driver.py:240-258)."""

@@ -16,6 +16,8 @@ at run time and executed in a namespace where
                      col_major_moe_gemm/test_moe_gemm.py:16-30) on a small bf16 case
   align_example.json : the worked example in the moe_align_block_size docstring
                      (v0_moe_fused.py:157-165), read from the docstring text
+  backward.npz     : `_pytorch_reference_backward` (kernels/MoE/group_GEMM/triton/testing/
+                     pytorch_reference_backwards.py:165-197) on three small cases
   quant_1x128.npz  : `_float8_groupwise_quant_kernel` (float8_groupwise_quant.py:20-50)
                      executed by Triton's CPU interpreter, if that is available
 
@@ -163,8 +165,35 @@ def golden_quant():
         print("quant_1x128.npz NOT written:", repr(exc))
 
 
+def golden_backward():
+    """`_pytorch_reference_backward` (kernels/MoE/group_GEMM/triton/testing/
+    pytorch_reference_backwards.py:165-197) pulled out of the reference file and run on the CPU in
+    fp32 on bf16-rounded inputs."""
+    path = os.path.join(REF, "kernels/MoE/group_GEMM/triton/testing/pytorch_reference_backwards.py")
+    fn = compile_function(find_function(path, "_pytorch_reference_backward"), {"torch": torch}, path)
+    out = {}
+    cases = [(4, 96, 64, 48, [30, 0, 41, 25], 51), (3, 200, 32, 72, [64, 100, 36], 52), (2, 128, 128, 64, [128, 0], 53)]
+    for i, (G, M, N, K, ms, seed) in enumerate(cases):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        w = (torch.randn(G * N, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+        dy = torch.randn(M, N * G, generator=g).to(torch.bfloat16)
+        m_sizes = torch.tensor(ms, dtype=torch.int32)
+        gx, gw = fn(dy.float(), x.float(), w.float(), m_sizes)
+        out[f"x{i}"], out[f"w{i}"], out[f"dy{i}"] = bits16(x), bits16(w), bits16(dy)
+        out[f"m_sizes{i}"] = m_sizes.numpy()
+        out[f"grad_x{i}"], out[f"grad_w{i}"] = gx.numpy().astype(np.float32), gw.numpy().astype(np.float32)
+    out["n_cases"] = np.array(len(cases))
+    np.savez_compressed(os.path.join(HERE, "backward.npz"), **out)
+    print("backward.npz:", len(cases), "cases")
+
+
 if __name__ == "__main__":
+    if "--only-backward" in sys.argv:
+        golden_backward()
+        sys.exit(0)
     golden_grouped()
     golden_torch_moe()
     golden_align_example()
     golden_quant()
+    golden_backward()
