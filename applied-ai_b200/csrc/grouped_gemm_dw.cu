@@ -78,6 +78,52 @@ __device__ __forceinline__ void build_padded_layout(const int32_t* m_sizes, int 
     }
 }
 
+// One 64x64 bf16 tile through shared memory, run by 256 threads.
+// Reads src[r][c] for r < rows_in, c < cols_in (zeros elsewhere) with 16-byte loads when the
+// tile is whole and aligned, writes dst[c][r] for c < rows_out, r < cols_out the same way.
+__device__ __forceinline__ void transpose_tile_64(const __nv_bfloat16* src, long long src_ld, int rows_in, int cols_in,
+                                                  __nv_bfloat16* dst, long long dst_ld, int rows_out, int cols_out,
+                                                  __nv_bfloat16 (*tile)[66]) {
+    const bool vec_in = rows_in > 0 && cols_in == 64 && (src_ld % 8) == 0 &&
+                        (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+    if (vec_in) {
+        for (int idx = threadIdx.x; idx < 64 * 8; idx += blockDim.x) {
+            const int r = idx >> 3, v = idx & 7;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (r < rows_in) raw = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * src_ld) + v);
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+            uint32_t* t = reinterpret_cast<uint32_t*>(&tile[r][v * 8]);  // rows are 132 bytes apart: 4-byte aligned
+            t[0] = w[0]; t[1] = w[1]; t[2] = w[2]; t[3] = w[3];
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x) {
+            const int r = idx >> 6, c = idx & 63;
+            tile[r][c] = (r < rows_in && c < cols_in) ? src[static_cast<size_t>(r) * src_ld + c] : __float2bfloat16(0.0f);
+        }
+    }
+    __syncthreads();
+    const bool vec_out = cols_out == 64 && (dst_ld % 8) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+    if (vec_out) {
+        for (int idx = threadIdx.x; idx < 64 * 8; idx += blockDim.x) {
+            const int c = idx >> 3, v = idx & 7;  // output row c, 8 consecutive output columns r = 8v..8v+7
+            if (c >= rows_out) continue;
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const unsigned short lo = *reinterpret_cast<const unsigned short*>(&tile[v * 8 + 2 * j][c]);
+                const unsigned short hi = *reinterpret_cast<const unsigned short*>(&tile[v * 8 + 2 * j + 1][c]);
+                w[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+            }
+            reinterpret_cast<uint4*>(dst + static_cast<size_t>(c) * dst_ld)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x) {
+            const int c = idx >> 6, r = idx & 63;
+            if (c < rows_out && r < cols_out) dst[static_cast<size_t>(c) * dst_ld + r] = tile[r][c];
+        }
+    }
+}
+
 // out[c, koff_g + i] = src[off_g + i, col0_g + c]  (i < m_g), zeros in the padding and in the
 // extra zero block.  src has `ld` elements per row; col0_g = g * col_group_stride.
 // grid: x = padded 64-column blocks (upper bound M/64 + G + 1), y = C / 64 (rounded up).
@@ -108,18 +154,10 @@ transpose_pad_kernel(const __nv_bfloat16* __restrict__ src, long long ld, long l
         valid = min(64, (row_off[g + 1] - row_off[g]) - i0);
     }
     // load 64 rows x 64 columns (zeros outside), transposed through shared memory
-    for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x) {
-        const int r = idx >> 6, c = idx & 63;
-        __nv_bfloat16 v = __float2bfloat16(0.0f);
-        if (r < valid && c0 + c < C)
-            v = src[static_cast<size_t>(row_off[g] + i0 + r) * ld + static_cast<size_t>(g) * col_group_stride + c0 + c];
-        tile[r][c] = v;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x) {
-        const int c = idx >> 6, r = idx & 63;
-        if (c0 + c < C) out[static_cast<size_t>(c0 + c) * mpad + (static_cast<size_t>(blk) << 6) + r] = tile[r][c];
-    }
+    const __nv_bfloat16* src_tile =
+        src + static_cast<size_t>(row_off[g] + i0) * ld + static_cast<size_t>(g) * col_group_stride + c0;
+    __nv_bfloat16* dst_tile = out + static_cast<size_t>(c0) * mpad + (static_cast<size_t>(blk) << 6);
+    transpose_tile_64(src_tile, ld, valid, min(64, C - c0), dst_tile, mpad, min(64, C - c0), 64, tile);
 }
 
 // Batched plain transpose: dst[b, c, r] = src[b, r, c]  (src [B, R, C], dst [B, C, R]).
@@ -128,16 +166,8 @@ transpose_batched_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* _
     __shared__ __nv_bfloat16 tile[64][66];
     const size_t base = static_cast<size_t>(blockIdx.z) * R * C;
     const int r0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
-    for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x) {
-        const int r = idx >> 6, c = idx & 63;
-        tile[r][c] = (r0 + r < R && c0 + c < C) ? src[base + static_cast<size_t>(r0 + r) * C + c0 + c]
-                                                  : __float2bfloat16(0.0f);
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x) {
-        const int c = idx >> 6, r = idx & 63;
-        if (r0 + r < R && c0 + c < C) dst[base + static_cast<size_t>(c0 + c) * R + r0 + r] = tile[r][c];
-    }
+    transpose_tile_64(src + base + static_cast<size_t>(r0) * C + c0, C, min(64, R - r0), min(64, C - c0),
+                      dst + base + static_cast<size_t>(c0) * R + r0, R, min(64, C - c0), min(64, R - r0), tile);
 }
 
 struct DwSmemTail {

@@ -35,9 +35,10 @@ WORKLOADS = {
     # one rank's share of the DeepSeek-V3 layer at 8-way expert parallelism: 32 experts, 32768 routed rows
     "c4_gate_up": (32, 32768, 4096, 7168),
     "c4_down": (32, 32768, 7168, 2048),
+    "c2_backward": (8, 16384, 4096, 7168),  # grad_x and grad_w of the C2 forward
 }
 WORKLOAD_KIND = {"c2": "bf16", "c5": "bf16", "c2_fp8_rowwise": "fp8_rowwise", "c2_fp8_blockwise": "fp8_blockwise",
-                 "c4_gate_up": "fp8_blockwise", "c4_down": "fp8_blockwise"}
+                 "c4_gate_up": "fp8_blockwise", "c4_down": "fp8_blockwise", "c2_backward": "bf16_backward"}
 
 
 def load_peaks():
@@ -243,6 +244,14 @@ def make_workload(name, rank, dev, cta_group):
         wl["step"] = lambda a=x: B.grouped_gemm(a, w, m_sizes, cta_group=cta_group)
         wl["ref_rows"] = lambda rows, e: x[rows].cpu().float() @ w[e].cpu().float().T
         wl["tol"] = 1e-2
+    elif kind == "bf16_backward":
+        from applied_ai_b200.tgroup_gemm_backwards import grouped_gemm_backward
+        gd = torch.Generator(device=dev).manual_seed(4242 + rank)
+        dy = torch.randn(M, N, generator=gd, device=dev).to(torch.bfloat16)
+        wl.update(x=x, w=w, act=[dy], elem=2)
+        wl["step"] = lambda a=dy: grouped_gemm_backward(a, x, w, m_sizes, cta_group=cta_group, check=False)[0]
+        wl["ref_rows"] = lambda rows, e: dy[rows].cpu().float() @ w[e].cpu().float()
+        wl["tol"] = 1e-2
     elif kind == "fp8_rowwise":
         xq, xs = B.quantize_fp8_row(x)
         wq, ws = B.quantize_fp8_row(w.reshape(G * N, K))
@@ -275,8 +284,8 @@ def make_workload(name, rank, dev, cta_group):
             return r
         wl["ref_rows"] = ref_rows
         wl["tol"] = 2e-2
-    wl["n_out"] = n_out
-    wl["flops"] = 2.0 * wl["rows"] * N * K
+    wl["n_out"] = K if kind == "bf16_backward" else n_out
+    wl["flops"] = (4.0 if kind == "bf16_backward" else 2.0) * wl["rows"] * N * K
     nonempty = int((m_sizes > 0).sum())
     act_bytes = sum(t.numel() * t.element_size() for t in wl["act"])
     wl["act_bytes"] = act_bytes
@@ -391,7 +400,7 @@ def run_ours(args):
             gbs = wl["alg_bytes"] / (ms_step * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": gbs / peaks["hbm_gbs"], "traffic": args.traffic, "peak_source": peaks["source"]}
-        elif wl["kind"] == "bf16":
+        elif wl["kind"] in ("bf16", "bf16_backward"):
             roof = {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": per_gpu / peaks["bf16_tflops"], "traffic": args.traffic,
                     "peak_source": peaks["source"] + " (burst cuBLAS bf16)",
@@ -403,7 +412,7 @@ def run_ours(args):
                     "peak_source": "measured in this run (torch._scaled_mm e4m3 8192^3, best of 10)"}
         cpu_rows = 1024 if M // G >= 1024 else max(8, M // G)
         cpu_tf, cpu_t, cpu_M = cpu_loop_tflops(min(G, 8), N, K, cpu_rows, repeats=3)
-        dtype = {"bf16": "bf16", "fp8_rowwise": "fp8_e4m3", "fp8_blockwise": "fp8_e4m3"}[wl["kind"]]
+        dtype = {"bf16": "bf16", "bf16_backward": "bf16", "fp8_rowwise": "fp8_e4m3", "fp8_blockwise": "fp8_e4m3"}[wl["kind"]]
         line = {
             "metric": "grouped_gemm_tflops", "value": tflops, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -421,7 +430,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": wl["act_bytes"] + G * 4, "d2h_bytes_per_step": M * wl["n_out"] * 2,
                     "ms_per_step": ms_e2e,
                     "note": "activations (+scales) and m_sizes from pinned host memory, weights resident"},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * (5 if wl["kind"] == "bf16_backward" else 1),
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
