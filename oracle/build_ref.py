@@ -6,7 +6,7 @@ setup.py:45-58 and the CUTLASS/CuTe headers that ship inside the Python environm
 baseline `bench.py --workload dense` times next to this package's dense mode and a second
 opinion for tests; the product never loads it.
 
-Needs the reference checkout ($APPLIED_AI_REFERENCE or /root/reference); without it the
+Needs the reference checkout (its path in $APPLIED_AI_REFERENCE); without it the
 function returns None and an already built library, if any, is used as is.
 """
 import os

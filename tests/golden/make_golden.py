@@ -1,6 +1,5 @@
 """Generates the golden fixtures of this directory by running the REFERENCE's own test
-code on the CPU.  Needs the reference checkout (default /root/reference, or
-$APPLIED_AI_REFERENCE); the fixtures it writes are committed so the tests need only them.
+code on the CPU.  Needs the reference checkout (its path in $APPLIED_AI_REFERENCE); the fixtures it writes are committed so the tests need only them.
 
 Nothing of the reference is copied: functions are pulled out of its files with `ast`
 at run time and executed in a namespace where
