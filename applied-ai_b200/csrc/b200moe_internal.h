@@ -42,6 +42,7 @@ struct GGParams {
     const float* c_in;             // fp32 epilogue: the C operand of alpha*acc + beta*C (same layout as y)
     float alpha, beta;
     uint32_t idesc;                // tcgen05 instruction descriptor (operand formats, tile shape)
+    uint32_t idesc_half;           // same with N = 128, for the split tiles of the last round
     int y_rows;                    // rows of y (bounds for row_map)
     long long ldy;                 // elements between consecutive rows of y
     long long y_col_group_stride;  // first column of group g's block is g * this (0: all groups share columns)

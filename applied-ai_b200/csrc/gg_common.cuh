@@ -137,6 +137,36 @@ __device__ __forceinline__ TileCoord locate_tile(int t, int& g, const int* tile_
     return c;
 }
 
+// The last, partial round of tiles.  With C clusters and T tiles, r = T mod C tiles remain
+// after the full rounds; when they would occupy at most half of the clusters, each is cut
+// into two 128-column halves so the round takes half as long.  Work item w < split_from is
+// tile w; the items after that are (tile, half) pairs.
+struct WorkSplit {
+    int split_from, total_work;
+};
+__device__ __forceinline__ WorkSplit make_work_split(int total_tiles, int num_clusters, bool allow) {
+    const int r = total_tiles % num_clusters;
+    WorkSplit ws;
+    if (allow && r > 0 && 2 * r <= num_clusters) {
+        ws.split_from = total_tiles - r;
+        ws.total_work = total_tiles + r;
+    } else {
+        ws.split_from = total_tiles;
+        ws.total_work = total_tiles;
+    }
+    return ws;
+}
+__device__ __forceinline__ void decode_work(int w, const WorkSplit& ws, int* tile, int* half) {
+    if (w < ws.split_from) {
+        *tile = w;
+        *half = -1;
+    } else {
+        const int h = w - ws.split_from;
+        *tile = ws.split_from + (h >> 1);
+        *half = h & 1;
+    }
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -273,7 +303,7 @@ __device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GG
 // TMA producer, run by ONE thread per CTA: for every tile of this cluster and every
 // 128-byte slice of K, wait for a free stage and fetch this CTA's 128 rows of x and its
 // share of the tile's two 128-row boxes of w[g] (rows nb0.. and nb1..).
-template <int CTAS, int LESS, bool SWIGLU>
+template <int CTAS, int LESS, bool SWIGLU, bool HALF = false>
 __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUtensorMap* tm_w, SmemTail* st,
                                               uint32_t ring_addr, const GGParams& p, uint32_t cta_rank,
                                               int cluster_id, int num_clusters, int elems_per_stage, int num_kb) {
@@ -284,11 +314,20 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
     const int total_tiles = st->total_tiles;
     int g = 0, stage = 0;
     uint32_t phase = 0;
-    for (int t = cluster_id; t < total_tiles; t += num_clusters) {
+    const WorkSplit ws = make_work_split(total_tiles, num_clusters, HALF && CTAS == 2);
+    for (int wk = cluster_id; wk < ws.total_work; wk += num_clusters) {
+        int t, half;
+        decode_work(wk, ws, &t, &half);
         const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
         const int row0 = tc.row0 + static_cast<int>(cta_rank) * kRowsPerCta;
-        const int nb0 = SWIGLU ? tc.n_idx * 128 : tc.n_idx * kTileN;
-        const int nb1 = SWIGLU ? p.n_out + tc.n_idx * 128 : tc.n_idx * kTileN + 128;
+        int nb0 = SWIGLU ? tc.n_idx * 128 : tc.n_idx * kTileN;
+        int nb1 = SWIGLU ? p.n_out + tc.n_idx * 128 : tc.n_idx * kTileN + 128;
+        if (HALF && half >= 0) {
+            // half tile (CTA pair only): each CTA still fetches a 128-row box of w, of which the
+            // N = 128 MMA uses the first 64 rows
+            nb0 = SWIGLU ? tc.n_idx * 128 + half * 64 : tc.n_idx * kTileN + half * 128;
+            nb1 = SWIGLU ? p.n_out + tc.n_idx * 128 + half * 64 : tc.n_idx * kTileN + half * 128 + 64;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
             if (!mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag)) {
                 report(p.status, kStatusTimeoutProducer);

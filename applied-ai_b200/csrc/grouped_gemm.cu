@@ -79,11 +79,12 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
     const uint32_t tmem_base = st->tmem_base;
     const int total_tiles = st->total_tiles;
     const int num_kb = (p.K + kElemsPerStage - 1) / kElemsPerStage;
+    const WorkSplit ws = make_work_split(total_tiles, num_clusters, CTAS == 2);
 
     if (warp == 0) {
         // ================= TMA producer (one thread per CTA)
         if (lane == 0)
-            producer_loop<CTAS, 0, EPI == 1>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters,
+            producer_loop<CTAS, 0, EPI == 1, true>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters,
                                           kElemsPerStage, num_kb);
     } else if (warp == 1) {
         // ================= MMA issuer (one thread of the leader CTA)
@@ -91,7 +92,8 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
             int stage = 0, buf = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
-            for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
+            for (int wk = cluster_id; ok && wk < ws.total_work; wk += num_clusters) {
+                const uint32_t idesc = wk < ws.split_from ? p.idesc : p.idesc_half;
                 if (!mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
                     report(p.status, kStatusTimeoutMmaAcc);
                     ok = false;
@@ -112,7 +114,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         // 32 bytes along K per MMA: +2 in the descriptor's 16-byte units.
-                        umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                        umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
                                          (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit<CTAS>(&st->empty[stage]);
@@ -135,7 +137,9 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
             CTAS == 1 ? smem_u32(&st->acc_empty[0]) : mapa_shared(smem_u32(&st->acc_empty[0]), 0);
         int g = 0, buf = 0;
         uint32_t acc_phase = 0;
-        for (int t = cluster_id; t < total_tiles; t += num_clusters) {
+        for (int wk = cluster_id; wk < ws.total_work; wk += num_clusters) {
+            int t, half;
+            decode_work(wk, ws, &t, &half);
             const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
             int ok = 1;
             if (lane == 0) ok = mbar_wait(&st->acc_full[buf], acc_phase, abort_flag) ? 1 : 0;
@@ -154,7 +158,11 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
             constexpr int kOutCols = EPI == 1 ? 128 : kTileN;  // output columns per tile
             constexpr int kOutElem = EPI == 2 ? 4 : 2;         // bytes per output element
             constexpr int kSlabCols = 128 / kOutElem;          // columns in one 128-byte staged run
-            const int col0 = tc.n_idx * kOutCols;              // first output column of the tile (within group)
+            // a half tile covers half of the tile's output columns; with SwiGLU its up columns
+            // sit 64 (not 128) accumulator columns after the gate columns
+            const int tile_cols = half >= 0 ? kOutCols / 2 : kOutCols;
+            const int up_off = half >= 0 ? 64 : 128;
+            const int col0 = tc.n_idx * kOutCols + (half > 0 ? kOutCols / 2 : 0);  // first output column (within group)
             // Destination row: the row itself, where the caller's row map sends it, or a row of
             // another rank's buffer.
             RowDest rd;
@@ -172,7 +180,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
             const bool to_peers = p.row_tags != nullptr;  // kernel-uniform
 
 #pragma unroll 1
-            for (int slab = 0; slab < kOutCols / kSlabCols; ++slab) {
+            for (int slab = 0; slab < tile_cols / kSlabCols; ++slab) {
                 const int scol = col0 + slab * kSlabCols;
                 if (scol >= p.n_out) break;  // warp-uniform: nothing left to store in this tile
 #pragma unroll
@@ -184,7 +192,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                     tmem_ld_32x32(t_acc + static_cast<uint32_t>(c * 32), v);
                     if constexpr (EPI == 1) {
                         uint32_t u[32];
-                        tmem_ld_32x32(t_acc + static_cast<uint32_t>(128 + c * 32), u);
+                        tmem_ld_32x32(t_acc + static_cast<uint32_t>(up_off + c * 32), u);
                         tmem_ld_wait(v);
                         tmem_ld_wait(u);
 #pragma unroll
@@ -348,6 +356,7 @@ int grouped_gemm_launch(const GGLaunch& a) {
     p.alpha = a.alpha;
     p.beta = a.beta;
     p.idesc = make_idesc(fp8, 128 * ctas, kTileN, a.is_f16 != 0);
+    p.idesc_half = make_idesc(fp8, 128 * ctas, kTileN / 2, a.is_f16 != 0);
 #define B200MOE_LAUNCH(EB, SC, EP)                                                          \
     (ctas == 1 ? launch_variant<EB, 1, SC, EP>(tm_x, tm_w, p, di.sms, a.stream)              \
                : launch_variant<EB, 2, SC, EP>(tm_x, tm_w, p, di.sms, a.stream))

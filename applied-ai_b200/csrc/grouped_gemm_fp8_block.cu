@@ -433,6 +433,7 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.alpha = 1.0f;
     p.beta = 0.0f;
     p.idesc = make_idesc(true, 128 * ctas, kTileN);
+    p.idesc_half = p.idesc;
     if (a.epilogue == 0)
         return ctas == 1 ? launch_block_variant<1, 0>(tm_x, tm_w, p, di.sms, a.stream)
                          : launch_block_variant<2, 0>(tm_x, tm_w, p, di.sms, a.stream);
