@@ -87,14 +87,16 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
             producer_loop<CTAS, 0, EPI == 1, true>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters,
                                           kElemsPerStage, num_kb);
     } else if (warp == 1) {
-        // ================= MMA issuer (one thread of the leader CTA)
-        if (lane == 0 && cta_rank == 0) {
+        // ================= MMA issuer (leader CTA; the warp walks the loop, one elected lane issues)
+        if (cta_rank == 0) {
+            const bool leader = elect_one();
             int stage = 0, buf = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             for (int wk = cluster_id; ok && wk < ws.total_work; wk += num_clusters) {
                 const uint32_t idesc = wk < ws.split_from ? p.idesc : p.idesc_half;
-                if (!mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
+                // waits are warp-collective so that every lane takes the same way out
+                if (!__all_sync(0xffffffffu, mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag))) {
                     report(p.status, kStatusTimeoutMmaAcc);
                     ok = false;
                     break;
@@ -102,7 +104,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kTileN);
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(&st->full[stage], phase, abort_flag)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&st->full[stage], phase, abort_flag))) {
                         report(p.status, kStatusTimeoutMmaFull);
                         ok = false;
                         break;
@@ -111,20 +113,24 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                     const uint32_t a_addr = ring_addr + stage * Cfg::kStageBytes;
                     const uint64_t a_desc = make_sw128_kmajor_desc(a_addr);
                     const uint64_t b_desc = make_sw128_kmajor_desc(a_addr + kABytes);
+                    if (leader) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        // 32 bytes along K per MMA: +2 in the descriptor's 16-byte units.
-                        umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
-                                         (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < 4; ++k) {
+                            // 32 bytes along K per MMA: +2 in the descriptor's 16-byte units.
+                            umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                                             (kb > 0 || k > 0) ? 1u : 0u);
+                        }
+                        umma_commit<CTAS>(&st->empty[stage]);
                     }
-                    umma_commit<CTAS>(&st->empty[stage]);
+                    __syncwarp();
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                umma_commit<CTAS>(&st->acc_full[buf]);
+                if (leader) umma_commit<CTAS>(&st->acc_full[buf]);
+                __syncwarp();
                 buf ^= 1;
                 if (buf == 0) acc_phase ^= 1u;
             }

@@ -198,6 +198,20 @@ __host__ __device__ constexpr uint32_t make_idesc(bool is_fp8, int mma_m, int mm
            (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
 
+// One lane of a converged warp.  The MMA issuer walks its loop with the whole warp so that
+// descriptors and addresses are computed in warp-uniform code, and only the tcgen05.mma /
+// tcgen05.commit instructions themselves sit under this predicate: issued from a branch on
+// the lane id, four MMAs and a commit took 400-600 cycles of the issuing thread; this way ~170.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // D[tmem] (+)= A[smem] * B[smem]^T, issued by ONE thread.
 template <int CTAS, bool FP8>
 __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
