@@ -283,20 +283,22 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && cta_rank == 0) {
+        // the whole warp walks the loop (warp-uniform descriptors), one elected lane issues
+        if (cta_rank == 0) {
+            const bool leader = elect_one();
             int stage = 0, buf = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
                 const int nkb = st->kcnt[t / tiles_per_group];
-                if (!mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag))) {
                     report(p.status, kStatusTimeoutMmaAcc);
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kTileN);
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(&st->full[stage], phase, abort_flag)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&st->full[stage], phase, abort_flag))) {
                         report(p.status, kStatusTimeoutMmaFull);
                         ok = false;
                         break;
@@ -305,17 +307,22 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                     const uint32_t a_addr = ring_addr + stage * Cfg::kStageBytes;
                     const uint64_t a_desc = make_sw128_kmajor_desc(a_addr);
                     const uint64_t b_desc = make_sw128_kmajor_desc(a_addr + kABytes);
+                    if (leader) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma<CTAS, false>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit<CTAS>(&st->empty[stage]);
+                        for (int k = 0; k < 4; ++k)
+                            umma<CTAS, false>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                                              (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_commit<CTAS>(&st->empty[stage]);
+                    }
+                    __syncwarp();
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                umma_commit<CTAS>(&st->acc_full[buf]);
+                if (leader) umma_commit<CTAS>(&st->acc_full[buf]);
+                __syncwarp();
                 buf ^= 1;
                 if (buf == 0) acc_phase ^= 1u;
             }

@@ -91,18 +91,20 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                                           num_kb);
       } else if (warp == 1) {
         // ================= MMA issuer: one K block per stage, one TMEM buffer per K block
-        if (lane == 0 && cta_rank == 0) {
+        // (the whole warp walks the loop so that descriptors are warp-uniform; one elected lane issues)
+        if (cta_rank == 0) {
+            const bool leader = elect_one();
             int stage = 0, buf = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             for (int t = cluster_id; ok && t < total_tiles; t += num_clusters) {
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&st->acc_empty[buf], acc_phase ^ 1u, abort_flag))) {
                         report(p.status, kStatusTimeoutMmaAcc);
                         ok = false;
                         break;
                     }
-                    if (!mbar_wait(&st->full[stage], phase, abort_flag)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&st->full[stage], phase, abort_flag))) {
                         report(p.status, kStatusTimeoutMmaFull);
                         ok = false;
                         break;
@@ -112,12 +114,15 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     const uint32_t a_addr = ring_addr + stage * Cfg::kStageBytes;
                     const uint64_t a_desc = make_sw128_kmajor_desc(a_addr);
                     const uint64_t b_desc = make_sw128_kmajor_desc(a_addr + kABytes);
+                    if (leader) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma<CTAS, true>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
-                    // One commit serves two waiters: the producer (stage free) and the promotion
-                    // warps (this K block's product is in TMEM) both watch empty[stage].
-                    umma_commit<CTAS>(&st->empty[stage]);
+                        for (int k = 0; k < 4; ++k)
+                            umma<CTAS, true>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, k > 0 ? 1u : 0u);
+                        // One commit serves two waiters: the producer (stage free) and the promotion
+                        // warps (this K block's product is in TMEM) both watch empty[stage].
+                        umma_commit<CTAS>(&st->empty[stage]);
+                    }
+                    __syncwarp();
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1u;
