@@ -315,6 +315,9 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
     int g = 0, stage = 0;
     uint32_t phase = 0;
     const WorkSplit ws = make_work_split(total_tiles, num_clusters, HALF && CTAS == 2);
+    // Called by the whole producer warp: coordinates and addresses are computed in warp-uniform
+    // code, one elected lane issues the copies.
+    const bool leader = elect_one();
     for (int wk = cluster_id; wk < ws.total_work; wk += num_clusters) {
         int t, half;
         decode_work(wk, ws, &t, &half);
@@ -329,7 +332,7 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
             nb1 = SWIGLU ? p.n_out + tc.n_idx * 128 + half * 64 : tc.n_idx * kTileN + half * 128 + 64;
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag)) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag))) {
                 report(p.status, kStatusTimeoutProducer);
                 return;
             }
@@ -339,17 +342,22 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
             const int kx = k0 + static_cast<int>(tc.g * p.x_col_group_stride);      // column of x it sits at
             if constexpr (CTAS == 1) {
                 const uint32_t bar = smem_u32(&st->full[stage]);
-                mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
-                tma_load_2d(tm_x, bar, a_dst, kx, row0);
-                tma_load_3d(tm_w, bar, b_dst, k0, nb0, tc.g);
-                tma_load_3d(tm_w, bar, b_dst + kSubBoxBytes, k0, nb1, tc.g);
+                if (leader) {
+                    mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                    tma_load_2d(tm_x, bar, a_dst, kx, row0);
+                    tma_load_3d(tm_w, bar, b_dst, k0, nb0, tc.g);
+                    tma_load_3d(tm_w, bar, b_dst + kSubBoxBytes, k0, nb1, tc.g);
+                }
             } else {
                 // Bytes of both CTAs are counted on the leader's barrier.
                 const uint32_t bar = mapa_shared(smem_u32(&st->full[stage]), 0);
-                if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
-                tma_load_2d_pair(tm_x, bar, a_dst, kx, row0);
-                tma_load_3d_pair(tm_w, bar, b_dst, k0, cta_rank == 0 ? nb0 : nb1, tc.g);
+                if (leader) {
+                    if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                    tma_load_2d_pair(tm_x, bar, a_dst, kx, row0);
+                    tma_load_3d_pair(tm_w, bar, b_dst, k0, cta_rank == 0 ? nb0 : nb1, tc.g);
+                }
             }
+            __syncwarp();
             if (++stage == Cfg::kStages) {
                 stage = 0;
                 phase ^= 1u;

@@ -82,9 +82,8 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
     const WorkSplit ws = make_work_split(total_tiles, num_clusters, CTAS == 2);
 
     if (warp == 0) {
-        // ================= TMA producer (one thread per CTA)
-        if (lane == 0)
-            producer_loop<CTAS, 0, EPI == 1, true>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters,
+        // ================= TMA producer (the warp walks the loop, one elected lane issues)
+        producer_loop<CTAS, 0, EPI == 1, true>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters,
                                           kElemsPerStage, num_kb);
     } else if (warp == 1) {
         // ================= MMA issuer (leader CTA; the warp walks the loop, one elected lane issues)

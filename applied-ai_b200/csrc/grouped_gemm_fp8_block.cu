@@ -86,8 +86,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     if (warp < 4) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
       if (warp == 0) {
-        if (lane == 0)
-            producer_loop<CTAS, 0, kSwiglu>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters, 128,
+        producer_loop<CTAS, 0, kSwiglu>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters, 128,
                                           num_kb);
       } else if (warp == 1) {
         // ================= MMA issuer: one K block per stage, one TMEM buffer per K block
