@@ -244,7 +244,9 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     const int total_tiles = st->invalid ? 0 : p.G * tiles_per_group;
 
     if (warp == 0) {
-        if (lane == 0) {
+        // TMA producer: the warp walks the loop, one elected lane issues the copies
+        {
+            const bool leader = elect_one();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -255,7 +257,7 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                 const int kcol0 = k_idx * kTileN;
                 const int koff = st->koff[g], nkb = st->kcnt[g];
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag))) {
                         report(p.status, kStatusTimeoutProducer);
                         ok = false;
                         break;
@@ -265,16 +267,21 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                     const int c0 = koff + kb * 64;
                     if constexpr (CTAS == 1) {
                         const uint32_t bar = smem_u32(&st->full[stage]);
-                        mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
-                        tma_load_2d(&tm_a, bar, a_dst, c0, row0);
-                        tma_load_3d(&tm_b, bar, b_dst, c0, kcol0, 0);
-                        tma_load_3d(&tm_b, bar, b_dst + kSubBoxBytes, c0, kcol0 + 128, 0);
+                        if (leader) {
+                            mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                            tma_load_2d(&tm_a, bar, a_dst, c0, row0);
+                            tma_load_3d(&tm_b, bar, b_dst, c0, kcol0, 0);
+                            tma_load_3d(&tm_b, bar, b_dst + kSubBoxBytes, c0, kcol0 + 128, 0);
+                        }
                     } else {
                         const uint32_t bar = mapa_shared(smem_u32(&st->full[stage]), 0);
-                        if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
-                        tma_load_2d_pair(&tm_a, bar, a_dst, c0, row0);
-                        tma_load_3d_pair(&tm_b, bar, b_dst, c0, kcol0 + static_cast<int>(cta_rank) * 128, 0);
+                        if (leader) {
+                            if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                            tma_load_2d_pair(&tm_a, bar, a_dst, c0, row0);
+                            tma_load_3d_pair(&tm_b, bar, b_dst, c0, kcol0 + static_cast<int>(cta_rank) * 128, 0);
+                        }
                     }
+                    __syncwarp();
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1u;
