@@ -223,6 +223,39 @@ def fp8_peak_tflops():
     return 2.0 * n ** 3 / (best * 1e-3) / 1e12
 
 
+def vendor_grouped_mm(wl, y_ours, iters=10):
+    """The bf16 grouped GEMM of the installed torch (`torch._grouped_mm`, a library kernel) on the same
+    resident inputs, as a second baseline next to the CPU loop.  Returns a dict for the JSON line; never
+    raises.  The FP8 counterpart (`torch._scaled_grouped_mm`) is not called: in this torch build its kernel
+    is compiled for another architecture and aborts on the device, which costs the process its context."""
+    try:
+        m_sizes = wl["m_sizes"]
+        offs = torch.cumsum(m_sizes, 0).to(torch.int32)
+        if wl["kind"] == "bf16":
+            x, w = wl["x"], wl["w"]
+            name = "torch._grouped_mm"
+            fn = lambda: torch._grouped_mm(x, w.transpose(-2, -1), offs=offs)
+        else:
+            return None
+        out = fn()
+        torch.cuda.synchronize()
+        rows = wl["rows"]
+        diff = float((out[:rows].float() - y_ours[:rows].float()).abs().max() / y_ours[:rows].float().abs().max())
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        return {"kind": name, "value": wl["flops"] / (ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": ms,
+                "max_rel_diff_vs_this_engine": diff, "note": "library kernel of the installed torch, same resident inputs"}
+    except Exception as exc:  # missing op, unsupported shape or dtype on this build
+        return {"kind": "torch grouped mm", "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
+
+
 def make_workload(name, rank, dev, cta_group):
     """Builds device-resident inputs and the step function of one workload."""
     import applied_ai_b200 as B
@@ -360,6 +393,8 @@ def run_ours(args):
     ms_total = ev0.elapsed_time(ev1)
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
 
+    vendor = vendor_grouped_mm(wl, y) if (rank == 0 and world == 1) else None
+
     # end to end: pinned host activations (and their scales) -> device, the public API call, result -> host,
     # every step.  Copies and compute of consecutive steps overlap the way a caller streaming batches
     # would run them: an upload stream, the compute stream and a download stream over two sets of buffers.
@@ -461,6 +496,8 @@ def run_ours(args):
             "gpu_launches": args.steps * (5 if wl["kind"] == "bf16_backward" else 1),
             "clocks": clocks,
         }
+        if vendor is not None:
+            line["vendor_baseline"] = vendor
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
