@@ -223,6 +223,14 @@ def fp8_peak_tflops():
     return 2.0 * n ** 3 / (best * 1e-3) / 1e12
 
 
+PROFILED_TRAFFIC_BYTES = {
+    "c2": 1.160e9,                # profiles/gg_kernel_bf16_c2_deepseek_gate_up.md
+    "c5": 750.5e6,                # profiles/gg_kernel_bf16_c5_skewed_routing.md
+    "c2_fp8_rowwise": 473.8e6,    # profiles/gg_kernel_fp8_rowwise_c2_shape.md
+    "c2_fp8_blockwise": 475.7e6,  # profiles/gg_fp8_block_kernel_c2_shape.md
+}
+
+
 def vendor_grouped_mm(wl, y_ours, iters=10):
     """The bf16 grouped GEMM of the installed torch (`torch._grouped_mm`, a library kernel) on the same
     resident inputs, as a second baseline next to the CPU loop.  Returns a dict for the JSON line; never
@@ -783,6 +791,10 @@ def main():
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture, echoed into the roofline object")
     args = ap.parse_args()
+    if args.traffic is None and args.cta_group == 0:
+        # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, one launch, from the ncu
+        # captures summarised under profiles/ (same workload and tiling); not measured in this run
+        args.traffic = PROFILED_TRAFFIC_BYTES.get(args.workload)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "dense":
