@@ -10,7 +10,8 @@ import sys
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
-LIB_PATH = os.path.join(PKG_DIR, "libb200moe.so")
+# B200MOE_LIBRARY: load another build of the library (e.g. one made with other nvcc flags) instead of the in-tree one
+LIB_PATH = os.environ.get("B200MOE_LIBRARY") or os.path.join(PKG_DIR, "libb200moe.so")
 SOURCES = ["capi.cu", "grouped_gemm.cu", "grouped_gemm_fp8_block.cu", "grouped_gemm_dw.cu", "moe_kernels.cu", "ep_kernels.cu", "selftest.cu"]
 HEADERS = ["b200moe_internal.h", "moe_kernels.h", "ptx.cuh", "gg_common.cuh", os.path.join("..", "..", "include", "b200moe.h")]
 NVCC_FLAGS = [
