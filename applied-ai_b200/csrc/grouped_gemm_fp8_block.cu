@@ -32,17 +32,18 @@ constexpr int kBlkStageBytes = 32 * 64;  // peer-store staging per warp: 32 rows
 // EPI: 0 plain, 1 SwiGLU -> bf16, 3 SwiGLU -> e4m3 with one fp32 scale per row and 128 columns
 //      (the 1x128 quantiser of float8_groupwise_quant.py:36-46 applied to the fp32 values in
 //      registers, so the intermediate never exists in bf16).
-// PEER: built for outputs that go to other GPUs' memory (row tags, plain epilogue, whole 128-column
-//      runs): ring stages are given up for a staging buffer of 32 rows x 256 bytes per warp; a thread
-//      writes its row's 128 results there and sends them with ONE asynchronous bulk copy, which the
-//      copy engine of the SM carries out while the warp goes on with the next tile.  Ordinary stores
-//      to a peer held the epilogue up: the down GEMM of the 8-GPU layer took twice its local time.
-template <int CTAS, int EPI, bool PEER = false>
+// BULK (EPI 0 and 1, outputs made of whole 16-byte aligned runs): ring stages are given up for a staging
+//      slot of 256 bytes per thread; a thread writes its row's results (128 bf16, or 64 after SwiGLU) there
+//      and sends them with ONE asynchronous bulk copy, which the SM's copy engine carries out while the
+//      warp goes on with the next tile.  With ordinary stores the epilogue held the promotion warps up:
+//      0.626 -> 0.531 ms on the K=2048 down GEMM of the DeepSeek-V3 shape with local output, and for rows
+//      that go to other GPUs' memory the down GEMM of the 8-GPU layer took twice its local time.
+template <int CTAS, int EPI, bool BULK = false>
 __global__ void __launch_bounds__(kBlkThreads, 1)
 gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                     const GGParams p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
-    constexpr int kLess = PEER ? (CTAS == 2 ? 2 : 1) : 0;
+    constexpr int kLess = BULK ? (CTAS == 2 ? 2 : 1) : 0;
     constexpr int kRun = 64;                 // bytes per staged row of the ordinary-store path
     constexpr int kBulkRowBytes = 256 + 16;  // staged row of the bulk path: 128 bf16 + 16 bytes against bank conflicts
     using Cfg = StageCfg<CTAS, kLess>;
@@ -297,27 +298,35 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                                                 (static_cast<size_t>(rd.drow) * p.ldy +
                                                  static_cast<size_t>(tc.g) * p.y_col_group_stride) * 2
                                           : nullptr;
-            uint4* const stage = sv.warp_stage + ew * ((PEER ? 32 * kBulkRowBytes : 32 * kRun) / 16);
-            if constexpr (PEER) {
-                // (PEER is built for EPI 0 and n_out % 128 == 0 only: the launcher sees to it)
-                const int col0 = tc.n_idx * kTileN + half * 128;
+            uint4* const stage = sv.warp_stage + ew * ((BULK ? 32 * kBulkRowBytes : 32 * kRun) / 16);
+            if constexpr (BULK) {
+                // (built for whole runs only: n_out % 128 == 0, aligned pitch; the launcher sees to it)
+                constexpr int kMine = EPI == 1 ? 64 : 128;  // results this thread holds for its row
+                const int col0 = EPI == 1 ? tc.n_idx * 128 + half * 64 : tc.n_idx * kTileN + half * 128;
                 if (col0 < p.n_out) {  // warp-uniform
-                    bulk_wait_read();  // the previous tile's copy has finished reading this staging row
+                    bulk_wait_read();  // the previous tile's copy has finished reading this staging slot
                     uint4* const my_stage = stage + lane * (kBulkRowBytes / 16);
 #pragma unroll
-                    for (int q = 0; q < 16; ++q)
-                        my_stage[q] = make_uint4(pack_bf16x2(acc[q * 8 + 0], acc[q * 8 + 1]),
-                                                 pack_bf16x2(acc[q * 8 + 2], acc[q * 8 + 3]),
-                                                 pack_bf16x2(acc[q * 8 + 4], acc[q * 8 + 5]),
-                                                 pack_bf16x2(acc[q * 8 + 6], acc[q * 8 + 7]));
+                    for (int q = 0; q < kMine / 8; ++q) {
+                        float f[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if constexpr (EPI == 1)
+                                f[j] = silu_mul(acc[q * 8 + j], acc[64 + q * 8 + j]);
+                            else
+                                f[j] = acc[q * 8 + j];
+                        }
+                        my_stage[q] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                                 pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+                    }
                     fence_async_smem();
                     if (store_ok) {
                         char* const dst = my_row + static_cast<size_t>(col0) * 2;
                         if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                            bulk_store(dst, smem_u32(my_stage), 256);
+                            bulk_store(dst, smem_u32(my_stage), kMine * 2);
                         } else {  // a destination buffer that is not 16-byte aligned: element stores
-                            for (int j = 0; j < 128; ++j)
-                                reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(acc[j]);
+                            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(my_stage);
+                            for (int j = 0; j < kMine; ++j) reinterpret_cast<__nv_bfloat16*>(dst)[j] = src[j];
                         }
                     }
                     bulk_commit();
@@ -377,7 +386,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
     }
 
-    if constexpr (PEER) bulk_wait_all();  // (no-op for threads that issued no copy)
+    if constexpr (BULK) bulk_wait_all();  // (no-op for threads that issued no copy)
     __syncwarp();
     if (*abort_flag) {
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
@@ -394,12 +403,12 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 #endif
 }
 
-template <int CTAS, int EPI, bool PEER = false>
+template <int CTAS, int EPI, bool BULK = false>
 static int launch_block_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const GGParams& p, int sms,
                                 cudaStream_t stream) {
-    auto kernel = gg_fp8_block_kernel<CTAS, EPI, PEER>;
-    constexpr size_t smem = gg_smem_bytes<CTAS, PEER ? (CTAS == 2 ? 2 : 1) : 0,
-                                           PEER ? kBlkEpiWarps * 32 * (256 + 16) : kBlkEpiWarps * kBlkStageBytes>();
+    auto kernel = gg_fp8_block_kernel<CTAS, EPI, BULK>;
+    constexpr size_t smem = gg_smem_bytes<CTAS, BULK ? (CTAS == 2 ? 2 : 1) : 0,
+                                           BULK ? kBlkEpiWarps * 32 * (256 + 16) : kBlkEpiWarps * kBlkStageBytes>();
     static_assert(smem <= 232448, "shared memory per CTA");
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -475,16 +484,22 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.beta = 0.0f;
     p.idesc = make_idesc(true, 128 * ctas, kTileN);
     p.idesc_half = p.idesc;
-    // rows to peers in whole, 16-byte aligned 256-byte segments: the bulk-copy build
-    if (a.epilogue == 0 && a.row_tags != nullptr && a.N % 128 == 0 && a.ldy % 8 == 0 && a.y_col_group_stride % 8 == 0)
-        return ctas == 1 ? launch_block_variant<1, 0, true>(tm_x, tm_w, p, di.sms, a.stream)
-                         : launch_block_variant<2, 0, true>(tm_x, tm_w, p, di.sms, a.stream);
-    if (a.epilogue == 0)
-        return ctas == 1 ? launch_block_variant<1, 0>(tm_x, tm_w, p, di.sms, a.stream)
-                         : launch_block_variant<2, 0>(tm_x, tm_w, p, di.sms, a.stream);
+    // outputs made of whole, 16-byte aligned runs leave through bulk copies
+    const bool bulk = p.n_out % 128 == 0 && a.ldy % 8 == 0 && a.y_col_group_stride % 8 == 0 &&
+                      (a.row_tags != nullptr || (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0);
     if (a.epilogue == 3)
         return ctas == 1 ? launch_block_variant<1, 3>(tm_x, tm_w, p, di.sms, a.stream)
                          : launch_block_variant<2, 3>(tm_x, tm_w, p, di.sms, a.stream);
+    if (a.epilogue == 0) {
+        if (bulk)
+            return ctas == 1 ? launch_block_variant<1, 0, true>(tm_x, tm_w, p, di.sms, a.stream)
+                             : launch_block_variant<2, 0, true>(tm_x, tm_w, p, di.sms, a.stream);
+        return ctas == 1 ? launch_block_variant<1, 0>(tm_x, tm_w, p, di.sms, a.stream)
+                         : launch_block_variant<2, 0>(tm_x, tm_w, p, di.sms, a.stream);
+    }
+    if (bulk)
+        return ctas == 1 ? launch_block_variant<1, 1, true>(tm_x, tm_w, p, di.sms, a.stream)
+                         : launch_block_variant<2, 1, true>(tm_x, tm_w, p, di.sms, a.stream);
     return ctas == 1 ? launch_block_variant<1, 1>(tm_x, tm_w, p, di.sms, a.stream)
                      : launch_block_variant<2, 1>(tm_x, tm_w, p, di.sms, a.stream);
 }
