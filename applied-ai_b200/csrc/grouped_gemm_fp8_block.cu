@@ -32,7 +32,7 @@ constexpr int kBlkStageBytes = 32 * 64;  // peer-store staging per warp: 32 rows
 // EPI: 0 plain, 1 SwiGLU -> bf16, 3 SwiGLU -> e4m3 with one fp32 scale per row and 128 columns
 //      (the 1x128 quantiser of float8_groupwise_quant.py:36-46 applied to the fp32 values in
 //      registers, so the intermediate never exists in bf16).
-// BULK (EPI 0 and 1, outputs made of whole 16-byte aligned runs): ring stages are given up for a staging
+// BULK (EPI 0 and 1 with outputs made of whole 16-byte aligned runs; EPI 3 always): ring stages are given up for a staging
 //      slot of 256 bytes per thread; a thread writes its row's results (128 bf16, or 64 after SwiGLU) there
 //      and sends them with ONE asynchronous bulk copy, which the SM's copy engine carries out while the
 //      warp goes on with the next tile.  With ordinary stores the epilogue held the promotion warps up:
@@ -68,9 +68,12 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     }
     // Mailbox through which the two warps that share 32 rows exchange their half-row maxima
     // (EPI 3): amax[slot][half][row] and a sequence word per (slot, half, lane quarter).
-    float* const mail_amax = reinterpret_cast<float*>(sv.warp_stage);
+    float* const mail_amax =
+        reinterpret_cast<float*>(sv.warp_stage) + (BULK ? kBlkEpiWarps * 32 * ((256 + 16) / 4) : 0);  // after the bulk slots
     volatile int* const mail_seq = reinterpret_cast<volatile int*>(mail_amax + 2 * 2 * 128);
-    if (threadIdx.x < 16) mail_seq[threadIdx.x] = 0;
+    if constexpr (EPI == 3) {
+        if (threadIdx.x < 16) mail_seq[threadIdx.x] = 0;
+    }
     __syncthreads();
     if (warp == 0) {
         build_tables_and_barriers<CTAS, kLess>(st, p, lane, kTileRows, kBlkEpiWarps * CTAS);
@@ -267,6 +270,11 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 const float scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
                 const float inv_scale = __fdiv_rn(1.0f, scale);  // one division per row; values use a multiply
                 const int col = tc.n_idx * 128 + half * 64;
+                uint4* q_slot = nullptr;
+                if constexpr (BULK) {
+                    bulk_wait_read();  // the previous tile's copy has finished reading this slot
+                    q_slot = sv.warp_stage + (ew * 32 + lane) * ((256 + 16) / 16);
+                }
                 if (row_ok && col < p.n_out) {
                     uint8_t* q_row = static_cast<uint8_t*>(p.y) + static_cast<size_t>(row) * p.ldy + col;
 #pragma unroll
@@ -284,10 +292,18 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                             }
                             w[i] = packed;
                         }
-                        *reinterpret_cast<uint4*>(q_row + c4 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                        if constexpr (BULK)
+                            q_slot[c4] = make_uint4(w[0], w[1], w[2], w[3]);
+                        else
+                            *reinterpret_cast<uint4*>(q_row + c4 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    if constexpr (BULK) {  // the row's 64 bytes in one asynchronous copy (the launcher checked alignment)
+                        fence_async_smem();
+                        bulk_store(q_row, smem_u32(q_slot), 64);
                     }
                     if (half == 0) p.y_scale_out[static_cast<size_t>(row) * (p.n_out / 128) + tc.n_idx] = scale;
                 }
+                if constexpr (BULK) bulk_commit();
                 continue;
             }
             // ---- store: the thread's row, its (up to) 128 output columns, 64 at a time through
@@ -408,7 +424,8 @@ static int launch_block_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w
                                 cudaStream_t stream) {
     auto kernel = gg_fp8_block_kernel<CTAS, EPI, BULK>;
     constexpr size_t smem = gg_smem_bytes<CTAS, BULK ? (CTAS == 2 ? 2 : 1) : 0,
-                                           BULK ? kBlkEpiWarps * 32 * (256 + 16) : kBlkEpiWarps * kBlkStageBytes>();
+                                           BULK ? kBlkEpiWarps * 32 * (256 + 16) + (EPI == 3 ? 2304 : 0)
+                                                : kBlkEpiWarps * kBlkStageBytes>();
     static_assert(smem <= 232448, "shared memory per CTA");
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -487,9 +504,9 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     // outputs made of whole, 16-byte aligned runs leave through bulk copies
     const bool bulk = p.n_out % 128 == 0 && a.ldy % 8 == 0 && a.y_col_group_stride % 8 == 0 &&
                       (a.row_tags != nullptr || (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0);
-    if (a.epilogue == 3)
-        return ctas == 1 ? launch_block_variant<1, 3>(tm_x, tm_w, p, di.sms, a.stream)
-                         : launch_block_variant<2, 3>(tm_x, tm_w, p, di.sms, a.stream);
+    if (a.epilogue == 3)  // (its argument checks above already demand aligned, whole 128-column runs)
+        return ctas == 1 ? launch_block_variant<1, 3, true>(tm_x, tm_w, p, di.sms, a.stream)
+                         : launch_block_variant<2, 3, true>(tm_x, tm_w, p, di.sms, a.stream);
     if (a.epilogue == 0) {
         if (bulk)
             return ctas == 1 ? launch_block_variant<1, 0, true>(tm_x, tm_w, p, di.sms, a.stream)

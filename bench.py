@@ -686,6 +686,9 @@ def run_layer(args):
             "config": {"workload": f"{args.workload}: MoE FFN layer T={T} H={H} I={I} E={E} top-{k} {mode}, "
                                    f"{t_loc} tokens and {e_loc} experts per GPU",
                        "l2": "weights per GPU exceed the 126 MiB L2",
+                       "intermediate": ("bf16" if mode == "bf16" else
+                                        "e4m3 + 1x128 scales written by the gate+up GEMM's epilogue" if ops.fuse_requant
+                                        else "bf16, then the separate 1x128 quantiser"),
                        "exchange": ("none (1 GPU)" if world == 1 else
                                     f"NCCL all_to_all_single (counts, payload, return), {layer.W} waves"
                                     if args.exchange == "nccl" else
@@ -786,8 +789,9 @@ def main():
                     help="expert-parallel layers: chunks of local experts whose exchange overlaps compute")
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="expert-parallel layers: NCCL all-to-all, or remote stores into peer memory")
-    ap.add_argument("--fuse-requant", action="store_true", dest="fuse_requant",
-                    help="FP8 layers: quantise the SwiGLU output inside the gate+up GEMM")
+    ap.add_argument("--fuse-requant", action=argparse.BooleanOptionalAction, default=True, dest="fuse_requant",
+                    help="FP8 layers: quantise the SwiGLU output inside the gate+up GEMM (default; "
+                         "--no-fuse-requant runs the separate quantiser on a bf16 intermediate)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture, echoed into the roofline object")
     args = ap.parse_args()
