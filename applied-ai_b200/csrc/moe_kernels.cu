@@ -393,17 +393,33 @@ combine_topk_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restri
         const int t = static_cast<int>(v / vec_per_row);
         const int c = static_cast<int>(v - static_cast<long long>(t) * vec_per_row) << 3;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < k; ++j) {
-            const int p = __ldg(inv_perm + static_cast<size_t>(t) * k + j);
-            if (p < 0 || p >= y_rows) continue;
-            const float wgt = weight ? __ldg(weight + static_cast<size_t>(t) * k + j) : 1.0f;
-            const uint4 r4 = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(p) * H + c);
-            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&r4);
+        // four rows at a time: their loads are all in flight before the first FMA (sum order stays j = 0, 1, ...)
+        for (int j0 = 0; j0 < k; j0 += 4) {
+            int pj[4];
+            float wj[4];
+            uint4 rj[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float2 f = __bfloat1622float2(r2[q]);
-                acc[2 * q] = fmaf(wgt, f.x, acc[2 * q]);
-                acc[2 * q + 1] = fmaf(wgt, f.y, acc[2 * q + 1]);
+            for (int u = 0; u < 4; ++u) {
+                const int j = j0 + u;
+                pj[u] = j < k ? __ldg(inv_perm + static_cast<size_t>(t) * k + j) : -1;
+                wj[u] = (j < k && weight) ? __ldg(weight + static_cast<size_t>(t) * k + j) : 1.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const bool live = pj[u] >= 0 && pj[u] < y_rows;
+                rj[u] = live ? *reinterpret_cast<const uint4*>(y + static_cast<size_t>(pj[u]) * H + c)
+                             : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (pj[u] < 0 || pj[u] >= y_rows) continue;
+                const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rj[u]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __bfloat1622float2(r2[q]);
+                    acc[2 * q] = fmaf(wj[u], f.x, acc[2 * q]);
+                    acc[2 * q + 1] = fmaf(wj[u], f.y, acc[2 * q + 1]);
+                }
             }
         }
         uint4 o4;
