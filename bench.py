@@ -226,7 +226,7 @@ def fp8_peak_tflops():
 PROFILED_TRAFFIC_BYTES = {
     "c2": 1.160e9,                # profiles/gg_kernel_bf16_c2_deepseek_gate_up.md
     "c5": 750.5e6,                # profiles/gg_kernel_bf16_c5_skewed_routing.md
-    "c2_fp8_rowwise": 473.8e6,    # profiles/gg_kernel_fp8_rowwise_c2_shape.md
+    "c2_fp8_rowwise": 471.0e6,    # profiles/gg_kernel_fp8_rowwise_c2_shape.md
     "c2_fp8_blockwise": 477.1e6,  # profiles/gg_fp8_block_kernel_c2_shape.md
 }
 
