@@ -71,6 +71,30 @@ SIGNATURES = {
     "b200moe_quant_1x128": [_c_vp, _c_int, _c_vp, _c_vp, _c_i64, _c_int, _c_vp],
 }
 
+# Kernels each entry point enqueues (for callers that report how many kernels of this library ran).
+KERNELS_PER_CALL = {
+    "b200moe_grouped_gemm_bf16": 1, "b200moe_grouped_gemm_fp8_rowwise": 1, "b200moe_grouped_gemm_fp8_blockwise": 1,
+    "b200moe_grouped_gemm_ex": 1, "b200moe_sm100_gemm_f16": 1, "b200moe_grouped_gemm_backward": 5,
+    "b200moe_route": 3, "b200moe_route_noalloc": 3, "b200moe_moe_align_block_size": 5, "b200moe_gather_rows": 1,
+    "b200moe_swiglu": 1, "b200moe_combine_topk": 1, "b200moe_quant_1x128": 1, "b200moe_ep_plan": 1,
+    "b200moe_ep_push": 1, "b200moe_selftest_wait_timeout": 1,
+}
+_launches = 0
+
+
+def launch_count():
+    """Kernels enqueued through this loader so far (sum of KERNELS_PER_CALL over the calls made)."""
+    return _launches
+
+
+def _counted(fn, n):
+    def call(*args):
+        global _launches
+        _launches += n
+        return fn(*args)
+    return call
+
+
 _lock = threading.Lock()
 _lib = None
 
@@ -111,6 +135,8 @@ def load(build_if_missing=True):
             fn = getattr(lib, name)  # AttributeError here = stale library
             fn.argtypes = argtypes
             fn.restype = _c_int
+            if name in KERNELS_PER_CALL:
+                setattr(lib, name, _counted(fn, KERNELS_PER_CALL[name]))
         _lib = lib
         return lib
 
