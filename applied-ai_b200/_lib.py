@@ -39,6 +39,7 @@ STATUS_NAMES = {
 # include/b200moe.h declares (a CPU test checks this).
 SIGNATURES = {
     "b200moe_version": [],
+    "b200moe_build_id": [],
     "b200moe_grouped_gemm_bf16": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_i64, _c_i64,
                                   _c_int, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
     "b200moe_grouped_gemm_fp8_rowwise": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
@@ -48,7 +49,7 @@ SIGNATURES = {
     "b200moe_grouped_gemm_ex": [_c_vp, _c_vp],
     "b200moe_ep_plan": [_c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp],
     "b200moe_ep_push": [_c_vp, _c_i64, _c_vp, _c_i64, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
-                        _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp],
+                        _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_vp],
     "b200moe_enable_peer_access": [_c_int],
     "b200moe_ipc_export": [_c_vp, _c_vp, ctypes.POINTER(ctypes.c_uint64)],
     "b200moe_ipc_open": [_c_vp, ctypes.POINTER(_c_vp)],
@@ -105,7 +106,7 @@ class GemmDesc(ctypes.Structure):
                 ("M", _c_int), ("N", _c_int), ("K", _c_int), ("G", _c_int), ("ldy", _c_i64),
                 ("y_col_group_stride", _c_i64), ("kind", _c_int), ("epilogue", _c_int), ("cta_group", _c_int),
                 ("y_rows", _c_int), ("y_row_map", _c_vp), ("y_row_tags", _c_vp), ("y_peer_bases", _c_vp),
-                ("n_peers", _c_int), ("status", _c_vp), ("y_scale_out", _c_vp)]
+                ("n_peers", _c_int), ("status", _c_vp), ("y_scale_out", _c_vp), ("y_fp32_out", _c_vp)]
 
 
 class B200MoeError(RuntimeError):
@@ -117,16 +118,23 @@ def lib_path():
 
 
 def load(build_if_missing=True):
-    """Load (building first if needed and allowed) and return the ctypes library."""
+    """Load and return the ctypes library.  A library that is missing, or that was built from
+    other sources than the ones on disk, is rebuilt first when that is allowed and nvcc is here;
+    otherwise loading fails loudly (never a silent run on an old binary)."""
     global _lib
     with _lock:
         if _lib is not None:
             return _lib
         path = _build.LIB_PATH
-        if not os.path.exists(path):
-            if not build_if_missing:
+        custom = bool(os.environ.get("B200MOE_LIBRARY"))  # a build the caller made with other flags: taken as is
+        if not custom and _build.is_stale():
+            if build_if_missing and _build.have_nvcc():
+                _build.build_library()
+            elif not os.path.exists(path):
                 raise ImportError(f"{path} is missing; run `python applied-ai_b200/build.py`")
-            _build.build_library()
+            else:
+                raise ImportError(f"{path} was built from other sources than those in {_build.CSRC}; "
+                                  "run `python applied-ai_b200/build.py`")
         try:
             lib = ctypes.CDLL(path)
         except OSError as exc:
@@ -137,6 +145,8 @@ def load(build_if_missing=True):
             fn.restype = _c_int
             if name in KERNELS_PER_CALL:
                 setattr(lib, name, _counted(fn, KERNELS_PER_CALL[name]))
+        if not custom and lib.b200moe_build_id() != _build.source_id():
+            raise ImportError(f"{path} does not carry the id of the sources in {_build.CSRC}; rebuild it")
         _lib = lib
         return lib
 

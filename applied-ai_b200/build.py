@@ -28,25 +28,54 @@ def _nvcc():
     raise RuntimeError("nvcc not found; libb200moe.so cannot be built")
 
 
+def source_id():
+    """31-bit id of the sources the library is built from (sha256 over their contents and the
+    nvcc flags).  It is compiled into the library (b200moe_build_id) and written next to it, so a
+    library older than the sources is recognised whatever the files' time stamps say."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for name in SOURCES + HEADERS:
+        with open(os.path.join(CSRC, name), "rb") as f:
+            h.update(name.encode() + b"\0" + f.read())
+    return int.from_bytes(h.digest()[:4], "big") & 0x7FFFFFFF
+
+
+def _id_path():
+    return LIB_PATH + ".id"
+
+
 def is_stale():
     if not os.path.exists(LIB_PATH):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
-    return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
+    try:
+        with open(_id_path()) as f:
+            return int(f.read().strip()) != source_id()
+    except (OSError, ValueError):
+        return True
+
+
+def have_nvcc():
+    try:
+        _nvcc()
+        return True
+    except RuntimeError:
+        return False
 
 
 def build_library(force=False, verbose=False):
-    """Compile the library if it is missing or older than its sources. Returns its path."""
+    """Compile the library if it is missing or was built from other sources. Returns its path."""
     if not force and not is_stale():
         return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
+    sid = source_id()
+    cmd = [_nvcc()] + NVCC_FLAGS + [f"-DB200MOE_BUILD_ID={sid}"] + (["-Xptxas", "-v"] if verbose else [])
     cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB_PATH]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:
         sys.stderr.write(res.stderr)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    with open(_id_path(), "w") as f:
+        f.write(str(sid))
     return LIB_PATH
 
 

@@ -39,6 +39,7 @@ struct GGParams {
     void* const* peer_y;           //   bases of y on every rank (device array, n_peers entries)
     int n_peers;
     float* y_scale_out;            // EPI 3: fp32 scales of the e4m3 output, [M, n_out/128]
+    float* y_f32_out;              // EPI 3, optional: the fp32 values that were quantised, [M, n_out]
     const float* c_in;             // fp32 epilogue: the C operand of alpha*acc + beta*C (same layout as y)
     float alpha, beta;
     uint32_t idesc;                // tcgen05 instruction descriptor (operand formats, tile shape)
@@ -65,6 +66,7 @@ struct GGLaunch {
     void* const* peer_y;
     int n_peers;
     float* y_scale_out;
+    float* y_f32_out;
     const float* c_in;
     float alpha, beta;
     int is_f16;      // 2-byte operands are IEEE half instead of bf16

@@ -23,6 +23,11 @@ extern "C" {
 
 int b200moe_version(void) { return 1; }
 
+#ifndef B200MOE_BUILD_ID
+#define B200MOE_BUILD_ID 0
+#endif
+int b200moe_build_id(void) { return B200MOE_BUILD_ID; }
+
 int b200moe_grouped_gemm_bf16(const void* x, const void* w, const int32_t* m_sizes, void* y, int M, int N, int K,
                               int G, int64_t ldy, int64_t y_col_group_stride, int epilogue, int cta_group,
                               const int32_t* y_row_map, int y_rows, int32_t* status, b200moe_stream_t stream) {
@@ -138,6 +143,7 @@ int b200moe_grouped_gemm_ex(const b200moe_gemm_desc* d, b200moe_stream_t stream)
         !(d->epilogue == B200MOE_EPI_SWIGLU_FP8 && d->kind == B200MOE_KIND_FP8_BLOCKWISE))
         return kErrBadArgument;
     a.y_scale_out = d->y_scale_out;
+    a.y_f32_out = d->y_fp32_out;
     switch (d->kind) {
         case B200MOE_KIND_BF16:
             a.elem_bytes = 2;
@@ -165,10 +171,12 @@ int b200moe_ep_plan(const int32_t* counts, int P, int E, int my_rank, int capaci
 int b200moe_ep_push(const void* part0, int64_t row_bytes0, const void* part1, int64_t row_bytes1,
                     const int32_t* perm, int top_k, const int32_t* offsets, const int32_t* dst_base, int R, int E,
                     int P, int my_rank, int capacity_rows, int tokens, void* const* peer_part0,
-                    void* const* peer_part1, int64_t* const* peer_tags, b200moe_stream_t stream) {
+                    void* const* peer_part1, int64_t* const* peer_tags, void* home_rows, int64_t home_row_bytes,
+                    b200moe_stream_t stream) {
     return ep_push_launch(part0, row_bytes0, part1, row_bytes1, perm, top_k, offsets, dst_base, R, E, P, my_rank,
                           capacity_rows, tokens, peer_part0, peer_part1,
-                          reinterpret_cast<long long* const*>(peer_tags), static_cast<cudaStream_t>(stream));
+                          reinterpret_cast<long long* const*>(peer_tags), home_rows, home_row_bytes,
+                          static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_enable_peer_access(int peer_device) { return enable_peer_access(peer_device); }

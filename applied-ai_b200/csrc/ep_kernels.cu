@@ -45,11 +45,13 @@ ep_plan_kernel(const int32_t* __restrict__ counts, int P, int E, int e_local, in
         for (int e = 0; e < e_local; ++e) {
             const int ge = d * e_local + e;
             dst_base[ge] = running + before[ge];
-            if (d == me) m_loc[e] = tot[ge];
+            // the owner computes the rows that fit: positions are in expert order, so what is
+            // dropped is a suffix and the group sizes stay consistent with the rows that arrive
+            if (d == me) m_loc[e] = max(0, min(tot[ge], cap - running));
             running += tot[ge];
         }
         // a destination that would overflow its buffer: rows past `cap` are dropped by the
-        // push kernel, and everybody learns about it here
+        // push kernel (their results count as zero), and everybody learns about it here
         if (running > cap && status != nullptr) atomicCAS(status, 0, kStatusCapacity);
     }
 }
@@ -62,7 +64,7 @@ ep_push_kernel(const uint8_t* __restrict__ part0, long long bytes0, const uint8_
                long long bytes1, const int32_t* __restrict__ perm, int k, const int32_t* __restrict__ offsets,
                const int32_t* __restrict__ dst_base, int R, int E, int e_local, int me, int cap, int tokens,
                uint8_t* const* __restrict__ peer0, uint8_t* const* __restrict__ peer1,
-               long long* const* __restrict__ peer_tag) {
+               long long* const* __restrict__ peer_tag, uint8_t* __restrict__ home, long long home_row_bytes) {
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
     // Every rank starts its walk over the (destination-sorted) rows at a different place, so
@@ -80,7 +82,15 @@ ep_push_kernel(const uint8_t* __restrict__ part0, long long bytes0, const uint8_
         const int row = __ldg(dst_base + ge) + (p - __ldg(offsets + ge));
         const int flat = __ldg(perm + p);
         const int tok = flat / k;
-        if (row < 0 || row >= cap || flat < 0 || tok >= tokens) continue;
+        if (row < 0 || row >= cap || flat < 0 || tok >= tokens) {
+            // a row its owner has no room for is never computed: its result row, which the combine
+            // reads from this rank's home buffer, is zeroed here instead of keeping an older step's values
+            if (home != nullptr) {
+                uint4* z = reinterpret_cast<uint4*>(home + static_cast<size_t>(p) * home_row_bytes);
+                for (int v = lane; v < static_cast<int>(home_row_bytes >> 4); v += 32) z[v] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            continue;
+        }
         {
             const uint4* src = reinterpret_cast<const uint4*>(part0 + static_cast<size_t>(tok) * bytes0);
             uint4* dst = reinterpret_cast<uint4*>(peer0[d] + static_cast<size_t>(row) * bytes0);
@@ -125,13 +135,15 @@ int ep_plan_launch(const int32_t* counts, int P, int E, int me, int cap, int32_t
 
 int ep_push_launch(const void* part0, long long bytes0, const void* part1, long long bytes1, const int32_t* perm,
                    int k, const int32_t* offsets, const int32_t* dst_base, int R, int E, int P, int me, int cap,
-                   int tokens, void* const* peer0, void* const* peer1, long long* const* peer_tag,
-                   cudaStream_t stream) {
+                   int tokens, void* const* peer0, void* const* peer1, long long* const* peer_tag, void* home,
+                   long long home_row_bytes, cudaStream_t stream) {
     if (part0 == nullptr || perm == nullptr || offsets == nullptr || dst_base == nullptr || peer0 == nullptr ||
         peer_tag == nullptr || k <= 0 || R < 0 || E <= 0 || P <= 0 || E % P != 0 || bytes0 <= 0 || (bytes0 & 15) ||
         (part1 != nullptr && (peer1 == nullptr || bytes1 <= 0 || (bytes1 & 3))))
         return kErrBadArgument;
     if ((reinterpret_cast<uintptr_t>(part0) & 15u) || (reinterpret_cast<uintptr_t>(part1) & 15u)) return kErrAlignment;
+    if (home != nullptr && (home_row_bytes <= 0 || (home_row_bytes & 15) || (reinterpret_cast<uintptr_t>(home) & 15u)))
+        return kErrAlignment;
     // rows of part 1 start at multiples of bytes1 inside 256-byte aligned buffers: 4-byte aligned at least
     if (R == 0) return 0;
     int blocks = (R + 7) / 8;
@@ -140,7 +152,8 @@ int ep_push_launch(const void* part0, long long bytes0, const void* part1, long 
                                                static_cast<const uint8_t*>(part1), bytes1, perm, k, offsets, dst_base,
                                                R, E, E / P, me, cap, tokens,
                                                reinterpret_cast<uint8_t* const*>(peer0),
-                                               reinterpret_cast<uint8_t* const*>(peer1), peer_tag);
+                                               reinterpret_cast<uint8_t* const*>(peer1), peer_tag,
+                                               static_cast<uint8_t*>(home), home_row_bytes);
     return static_cast<int>(cudaGetLastError());
 }
 

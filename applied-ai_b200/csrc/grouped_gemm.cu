@@ -301,8 +301,9 @@ static int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, cons
 }
 
 int grouped_gemm_launch(const GGLaunch& a) {
-    if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0 || a.x == nullptr || a.w == nullptr || a.y == nullptr ||
-        (a.m_sizes == nullptr && a.G != 1))
+    // y may be null when every row leaves through (rank, row) tags: the peer table names the buffers
+    if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0 || a.x == nullptr || a.w == nullptr ||
+        (a.y == nullptr && a.row_tags == nullptr) || (a.m_sizes == nullptr && a.G != 1))
         return kErrBadArgument;
     if (a.G > kMaxGroups) return kErrTooManyGroups;
     if (a.elem_bytes != 1 && a.elem_bytes != 2) return kErrBadArgument;
@@ -360,6 +361,7 @@ int grouped_gemm_launch(const GGLaunch& a) {
     const int ctas = a.cta_group == 1 ? 1 : a.cta_group == 2 ? 2 : (a.M / a.G >= 192 ? 2 : 1);
     const bool fp8 = a.elem_bytes == 1;
     p.y_scale_out = nullptr;
+    p.y_f32_out = nullptr;
     p.c_in = a.c_in;
     p.alpha = a.alpha;
     p.beta = a.beta;

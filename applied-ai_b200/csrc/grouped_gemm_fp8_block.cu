@@ -267,9 +267,15 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 }
                 __threadfence_block();
                 amax = fmaxf(amax, mail_amax[(slot * 2 + (half ^ 1)) * 128 + rix]);
+                // the quantiser's own formula (float8_groupwise_quant.py:39-46), IEEE division included, so
+                // that the bytes equal those of quant_1x128_kernel run on these fp32 values
                 const float scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
-                const float inv_scale = __fdiv_rn(1.0f, scale);  // one division per row; values use a multiply
                 const int col = tc.n_idx * 128 + half * 64;
+                if (p.y_f32_out != nullptr && row_ok && col < p.n_out) {  // optional copy of the values quantised
+                    float4* f_row = reinterpret_cast<float4*>(p.y_f32_out + static_cast<size_t>(row) * p.n_out + col);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) f_row[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                }
                 uint4* q_slot = nullptr;
                 if constexpr (BULK) {
                     bulk_wait_read();  // the previous tile's copy has finished reading this slot
@@ -285,7 +291,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                             uint32_t packed = 0;
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                float v = f[c4 * 16 + i * 4 + j] * inv_scale;
+                                float v = __fdiv_rn(f[c4 * 16 + i * 4 + j], scale);
                                 v = fminf(fmaxf(v, -448.0f), 448.0f);
                                 packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3))
                                           << (8 * j);
@@ -451,13 +457,17 @@ static int launch_block_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w
 }
 
 int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
-    if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0 || a.x == nullptr || a.w == nullptr || a.y == nullptr ||
-        a.m_sizes == nullptr || a.x_scale == nullptr || a.w_scale == nullptr)
+    // y may be null when every row leaves through (rank, row) tags: the peer table names the buffers
+    if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0 || a.x == nullptr || a.w == nullptr ||
+        (a.y == nullptr && a.row_tags == nullptr) || a.m_sizes == nullptr || a.x_scale == nullptr ||
+        a.w_scale == nullptr)
         return kErrBadArgument;
     if (a.G > kMaxGroups) return kErrTooManyGroups;
     if (a.K % 128 != 0) return kErrAlignment;  // whole scale blocks along K
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.w) & 15u)) return kErrAlignment;
     if (a.epilogue != 0 && a.epilogue != 1 && a.epilogue != 3) return kErrBadArgument;
+    if (a.epilogue == 3 && a.y_f32_out != nullptr && (reinterpret_cast<uintptr_t>(a.y_f32_out) & 15u) != 0)
+        return kErrAlignment;
     if (a.epilogue == 3 && (a.y_scale_out == nullptr || a.row_map != nullptr || a.row_tags != nullptr ||
                             a.y_col_group_stride != 0 || (a.ldy & 15) != 0 ||
                             (reinterpret_cast<uintptr_t>(a.y) & 15u) != 0))
@@ -494,6 +504,7 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.n_out = a.epilogue != 0 ? a.N / 2 : a.N;
     p.n_tiles = a.epilogue != 0 ? (p.n_out + 127) / 128 : (p.n_out + kTileN - 1) / kTileN;
     p.y_scale_out = a.y_scale_out;
+    p.y_f32_out = a.epilogue == 3 ? a.y_f32_out : nullptr;
 
     // Auto tiling: this kernel is bound by the promotion round trip, not by the MMA, so CTA pairs buy nothing
     // until the padding of 128-row tiles stops mattering.  32 ragged groups, N=4096, K=7168, single vs pair:

@@ -34,8 +34,8 @@ int ep_plan_launch(const int32_t* counts, int P, int E, int me, int cap, int32_t
                    int32_t* status, cudaStream_t stream);
 int ep_push_launch(const void* part0, long long bytes0, const void* part1, long long bytes1, const int32_t* perm,
                    int k, const int32_t* offsets, const int32_t* dst_base, int R, int E, int P, int me, int cap,
-                   int tokens, void* const* peer0, void* const* peer1, long long* const* peer_tag,
-                   cudaStream_t stream);
+                   int tokens, void* const* peer0, void* const* peer1, long long* const* peer_tag, void* home,
+                   long long home_row_bytes, cudaStream_t stream);
 int enable_peer_access(int peer_device);
 int ipc_open(const void* handle_bytes, void** base);
 int ipc_export(const void* dev_ptr, void* handle_out64, unsigned long long* offset_out);

@@ -99,6 +99,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // Asynchronous copy of `bytes` (multiple of 16; both addresses 16-byte aligned) from this CTA's
 // shared memory to global memory, which may be another GPU's memory mapped into this process.
 // The copy belongs to the issuing thread's bulk async-group.
+// Invariant of this library: peer memory is reached by ordinary stores and by this store-side
+// copy only.  No load (plain, TMA or bulk) has a peer address as its source, and no copy in
+// either direction carries a .multicast::cluster qualifier.
 __device__ __forceinline__ void bulk_store(void* dst_global, uint32_t src_smem, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_global), "r"(src_smem),
                  "r"(bytes)

@@ -207,10 +207,13 @@ class ExpertParallelMoE:
                  hidden_size=None, capacity_factor=1.5):
         """exchange="nccl": all_to_all_single collectives (rows land in local buffers first).
         exchange="peer": rows are written straight into the owner's memory by the sender's push
-        kernel and come home through the down GEMM's store (plain stores over NVLink, CUDA IPC
-        mappings); needs max_tokens (per rank), top_k and hidden_size up front because the
+        kernel and come home through the down GEMM's store (ordinary stores or non-multicast
+        shared->global bulk copies over NVLink into CUDA IPC mappings; peer memory is never read); needs max_tokens (per rank), top_k and hidden_size up front because the
         shared buffers are built once, and a receive capacity of capacity_factor times the
-        rows a rank sends.  No host synchronisation happens in that mode."""
+        rows a rank sends.  No host synchronisation happens in that mode, so a routing skew that
+        overflows a rank's receive buffer cannot raise inside forward(): the surplus rows are
+        dropped (they contribute zero to their tokens), status 24 is recorded on the device, and
+        raise_on_status() reports it."""
         self.ops = ops
         self.group = group
         self.E = int(num_experts)
@@ -281,7 +284,7 @@ class ExpertParallelMoE:
                                  pb.part_row_bytes[1] if p1 is not None else 0, perm.data_ptr(), k,
                                  offsets.data_ptr(), dst_base.data_ptr(), R, self.E, P, pb.me, pb.cap, T,
                                  pb.tables[0].data_ptr(), pb.tables[1].data_ptr() if p1 is not None else 0,
-                                 pb.tables[len(parts)].data_ptr(), stream)
+                                 pb.tables[len(parts)].data_ptr(), pb.y_home.data_ptr(), 2 * H, stream)
         _lib.check(rc, "ep_push")
         mark("push")
         dist.all_reduce(pb.sync, group=self.group)          # every rank's rows have landed everywhere
@@ -299,6 +302,17 @@ class ExpertParallelMoE:
             torch.cuda.synchronize()
             self.timings = [(marks[i][0], marks[i - 1][1].elapsed_time(marks[i][1])) for i in range(1, len(marks))]
         return out
+
+    def raise_on_status(self):
+        """Deferred check of everything this layer has enqueued on the current device so far.  The
+        layer itself never synchronises with the host; call this wherever a synchronisation is
+        acceptable (after a step, every N steps, before results are trusted).  Raises
+        B200MoeError when a rank's receive buffer overflowed (status 24: rows past the capacity
+        were dropped, their experts' contributions are missing from the outputs of that step — build the layer with a larger
+        capacity_factor, or use exchange="nccl", which sizes its buffers per step) or when a
+        device-side wait ran out; ValueError for invalid expert ids."""
+        from . import groupgemm as gg
+        gg.pending_status()
 
     def _key_table(self, device):
         """Sort key of every global expert: (wave, destination rank, expert inside the wave), so

@@ -14,12 +14,15 @@ unit_tests.py:168-212): RuntimeError for shape/dtype/contiguity problems, ValueE
 for a group count that does not fit `w`, ValueError for group sizes the device
 rejects (negative, or adding up to more rows than x has).
 """
+import threading
+
 import torch
 
 from . import _lib
 
 _default_check = True
-_status_words = {}
+_status_words = {}          # (device index, stream handle) -> 4-byte status word on that device
+_state_lock = threading.Lock()
 
 
 def set_default_check(flag):
@@ -30,13 +33,46 @@ def set_default_check(flag):
     _default_check = bool(flag)
 
 
+def _device_index(device):
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
 def _status_word(device):
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    word = _status_words.get(key)
-    if word is None:
-        word = torch.zeros(1, dtype=torch.int32, device=device)
-        _status_words[key] = word
+    """The status word kernels launched on (device, its current stream) report into.  One word
+    per stream, so that calls issued on different streams or from different host threads never
+    share one (a word is sticky: the first code written stays until it is read and cleared)."""
+    idx = _device_index(device)
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    with _state_lock:
+        word = _status_words.get(key)
+        if word is None:
+            with torch.cuda.stream(torch.cuda.current_stream(idx)):
+                word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+            _status_words[key] = word
     return word
+
+
+def pending_status(device=None):
+    """Deferred check for callers that run with check=False: synchronises, reads every status
+    word of `device` (default: the current device), clears the ones that are set and raises for
+    the first code found — ValueError for invalid group sizes / expert ids, B200MoeError for the
+    rest (a device-side wait that ran out, an expert-parallel receive buffer that overflowed).
+    Returns None when nothing is pending."""
+    idx = torch.cuda.current_device() if device is None else _device_index(torch.device(device))
+    with _state_lock:
+        words = [w for (d, _), w in _status_words.items() if d == idx]
+    torch.cuda.synchronize(idx)
+    first = 0
+    for w in words:
+        code = int(w.item())
+        if code:
+            w.zero_()
+            first = first or code
+    if first:
+        msg = f"pending device status: {_lib.describe_status(first)} (status {first})"
+        if first == 1:
+            raise ValueError(msg)
+        raise _lib.B200MoeError(msg)
 
 
 def raise_on_status(word, what):
@@ -205,13 +241,16 @@ KIND_BF16, KIND_FP8_ROWWISE, KIND_FP8_BLOCKWISE = 0, 1, 2
 
 
 def grouped_gemm_ex(kind, x, w, m_sizes, *, x_scale=None, w_scale=None, epilogue="none", cta_group=0, y=None,
-                    out_row_map=None, out_row_tags=None, peer_bases=None, n_peers=0, out_rows=None, check=False):
+                    out_row_map=None, out_row_tags=None, peer_bases=None, n_peers=0, out_rows=None, check=False,
+                    return_fp32=False):
     """Struct-described grouped GEMM (b200moe_grouped_gemm_ex).  Besides everything the plain
     entry points do, result rows can be sent to (rank, row) destinations: out_row_tags int64 [M]
     = (rank << 32) | row and peer_bases = int64 device tensor of n_peers base addresses of bf16
     buffers with out_rows rows each (this rank's own buffer included).  Returns y, or None when
     rows go to peer buffers.  epilogue="swiglu_fp8" (block-wise kind): returns (e4m3 [M, N/2],
-    fp32 scales [M, N/256]) — silu(gate)*up quantised 1x128 inside the GEMM."""
+    fp32 scales [M, N/256]) — silu(gate)*up quantised 1x128 inside the GEMM with the formula of
+    float8_groupwise_quantize (IEEE division); return_fp32=True appends the fp32 values [M, N/2]
+    that were quantised, so a caller can check the bytes against the stand-alone quantiser."""
     import ctypes
     m_sizes, G, M, N, K = _prepare(x, w, m_sizes, torch.bfloat16 if kind == KIND_BF16 else torch.float8_e4m3fn)
     epi = {"none": 0, "swiglu": 1, "swiglu_fp8": 3}[epilogue]
@@ -224,6 +263,8 @@ def grouped_gemm_ex(kind, x, w, m_sizes, *, x_scale=None, w_scale=None, epilogue
         y = torch.empty((M, n_out), device=x.device, dtype=torch.float8_e4m3fn)
         y_scale = torch.empty((M, n_out // 128), device=x.device, dtype=torch.float32)
         d.y_scale_out = y_scale.data_ptr()
+        y_f32 = torch.empty((M, n_out), device=x.device, dtype=torch.float32) if return_fp32 else None
+        d.y_fp32_out = 0 if y_f32 is None else y_f32.data_ptr()
     d.x, d.w, d.m_sizes = x.data_ptr(), w.data_ptr(), m_sizes.data_ptr()
     d.x_scale = 0 if x_scale is None else x_scale.data_ptr()
     d.w_scale = 0 if w_scale is None else w_scale.data_ptr()
@@ -238,7 +279,7 @@ def grouped_gemm_ex(kind, x, w, m_sizes, *, x_scale=None, w_scale=None, epilogue
         _require(peer_bases is not None and peer_bases.dtype == torch.int64 and n_peers > 0 and out_rows,
                  "peer_bases (int64 device tensor), n_peers and out_rows are needed with out_row_tags")
         d.y_row_tags, d.y_peer_bases, d.n_peers, d.y_rows = out_row_tags.data_ptr(), peer_bases.data_ptr(), n_peers, out_rows
-        d.y = peer_bases.data_ptr()  # not dereferenced as y; must be non-null
+        d.y = 0  # every row goes to a peer buffer
     else:
         if y is None:
             y = torch.empty((M if out_rows is None else out_rows, n_out), device=x.device, dtype=torch.bfloat16)
@@ -253,5 +294,5 @@ def grouped_gemm_ex(kind, x, w, m_sizes, *, x_scale=None, w_scale=None, epilogue
         if check:
             raise_on_status(word, "grouped_gemm_ex")
     if epi == 3:
-        return y, y_scale
+        return (y, y_scale, y_f32) if return_fp32 else (y, y_scale)
     return None if out_row_tags is not None else y

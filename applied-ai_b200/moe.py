@@ -21,11 +21,15 @@ def _stream(t):
 
 
 def _workspace(device, nbytes):
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
+    """Scratch buffer of (device, its current stream): kernels of one stream run in order and may
+    share it; two streams (or two host threads on their own streams) never get the same one."""
+    idx = _gg._device_index(device)
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    with _gg._state_lock:
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+            _workspaces[key] = ws
     return ws
 
 

@@ -50,6 +50,10 @@ typedef void* b200moe_stream_t;
 #define B200MOE_CTA_AUTO 0    /* 1 = one CTA per 128x256 tile, 2 = a CTA pair per 256x256 tile */
 
 int b200moe_version(void);
+/* Id of the source files this binary was compiled from (0 when the build did not set one).
+ * The Python loader compares it with the sources on disk and refuses a library that does
+ * not match them.  No counterpart in the reference (its kernels are compiled on first use). */
+int b200moe_build_id(void);
 
 /* y[rows of group g, g*y_col_group_stride + (0..N)] = x[rows of group g, :] @ w[g]^T
  * x [M,K] bf16 row-major, w [G,N,K] bf16 row-major, m_sizes [G] int32 (device; zeros
@@ -96,7 +100,9 @@ int b200moe_grouped_gemm_fp8_blockwise(const void* xq, const void* wq, const flo
  * plus a second way to place result rows — y_row_tags[r] = (rank << 32) | row sends result
  * row r to row `row` of y_peer_bases[rank] (bf16, pitch ldy, y_rows rows each), which may
  * be another GPU's memory mapped into this process: the return leg of the expert-parallel
- * exchange happens inside the GEMM's store, as plain stores over NVLink.  No counterpart
+ * exchange happens inside the GEMM's store over NVLink: ordinary st.global from the bf16
+ * kernel, shared->global bulk copies (cp.async.bulk, never multicast) from the block-wise FP8
+ * kernel.  Peer memory is only ever a store destination: no load of any kind reads it.  No counterpart
  * in the reference (it has no distributed code). */
 #define B200MOE_KIND_BF16 0
 #define B200MOE_KIND_FP8_ROWWISE 1
@@ -105,7 +111,7 @@ typedef struct b200moe_gemm_desc {
     const void* x;            /* [M, K] */
     const void* w;            /* [G, N, K] */
     const int32_t* m_sizes;   /* [G] device */
-    void* y;                  /* bf16 output (unused when y_row_tags is set) */
+    void* y;                  /* bf16 output (may be NULL when y_row_tags is set) */
     const float* x_scale;     /* FP8 kinds */
     const float* w_scale;
     int M, N, K, G;
@@ -120,6 +126,8 @@ typedef struct b200moe_gemm_desc {
     int n_peers;
     int32_t* status;
     float* y_scale_out;       /* B200MOE_EPI_SWIGLU_FP8: scales of the quantised output */
+    float* y_fp32_out;        /* B200MOE_EPI_SWIGLU_FP8, optional (NULL: off): the fp32 silu(gate)*up values
+                                 [M, N/2] that were quantised, 16-byte aligned; for checking the quantiser */
 } b200moe_gemm_desc;
 int b200moe_grouped_gemm_ex(const b200moe_gemm_desc* desc, b200moe_stream_t stream);
 
@@ -132,7 +140,11 @@ int b200moe_grouped_gemm_ex(const b200moe_gemm_desc* desc, b200moe_stream_t stre
  * b200moe_ep_push: for every routed row p (sorted by global expert: perm, offsets from
  * b200moe_route) copy its token's bytes (part0, row size a multiple of 16, and optionally
  * part1, row size a multiple of 4) into the owner's buffers peer_part0[d] / peer_part1[d] at row dst_base[e] + i and
- * write peer_tags[d][row] = (my_rank << 32) | p.  Rows past capacity_rows are dropped.
+ * write peer_tags[d][row] = (my_rank << 32) | p.  Rows past capacity_rows are dropped: the owner's
+ * m_local counts only the rows that fit (a prefix in expert order), the sender zeroes the dropped
+ * row's result in its own home buffer (home_rows: [R] rows of home_row_bytes bytes, a multiple of
+ * 16; may be NULL), so the layer's output then lacks those experts' contributions, and
+ * B200MOE_SCAPACITY in the status word says so.
  * The peer_* arrays are DEVICE arrays of P pointers into buffers of capacity_rows rows on
  * each rank, mapped into this process (CUDA IPC); call b200moe_enable_peer_access for each
  * peer device once.  The caller orders "all pushes done" before the GEMMs with a
@@ -142,7 +154,8 @@ int b200moe_ep_plan(const int32_t* counts, int P, int E, int my_rank, int capaci
 int b200moe_ep_push(const void* part0, int64_t row_bytes0, const void* part1, int64_t row_bytes1,
                     const int32_t* perm, int top_k, const int32_t* offsets, const int32_t* dst_base, int R, int E,
                     int P, int my_rank, int capacity_rows, int tokens, void* const* peer_part0,
-                    void* const* peer_part1, int64_t* const* peer_tags, b200moe_stream_t stream);
+                    void* const* peer_part1, int64_t* const* peer_tags, void* home_rows, int64_t home_row_bytes,
+                    b200moe_stream_t stream);
 int b200moe_enable_peer_access(int peer_device);
 /* b200moe_ipc_export: the 64-byte IPC handle of the cudaMalloc allocation containing dev_ptr
  * and dev_ptr's byte offset in it.  b200moe_ipc_open: map such an allocation into this

@@ -6,8 +6,9 @@ setup.py:45-58 and the CUTLASS/CuTe headers that ship inside the Python environm
 baseline `bench.py --workload dense` times next to this package's dense mode and a second
 opinion for tests; the product never loads it.
 
-Needs the reference checkout (its path in $APPLIED_AI_REFERENCE); without it the
-function returns None and an already built library, if any, is used as is.
+Needs the reference checkout (its path in $APPLIED_AI_REFERENCE, else a directory named
+`reference` beside this repository); without it the function returns None and an already
+built library, if any, is used as is.
 """
 import os
 import shutil
@@ -31,7 +32,8 @@ def _cutlass_include():
 
 
 def build_reference_gemm(force=False):
-    ref = os.environ.get("APPLIED_AI_REFERENCE", "/root/reference")
+    # the checkout named by the environment, else one that sits beside this repository
+    ref = os.environ.get("APPLIED_AI_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     src = os.path.join(ref, "kernels/blackwell/cute_gemm_02_tma/sm100_gemm.cu")
     if not os.path.exists(src):
         return LIB if os.path.exists(LIB) else None

@@ -15,6 +15,10 @@ at run time and executed in a namespace where
                      col_major_moe_gemm/test_moe_gemm.py:16-30) on a small bf16 case
   align_example.json : the worked example in the moe_align_block_size docstring
                      (v0_moe_fused.py:157-165), read from the docstring text
+  grouped_fp8_rowwise.npz : the same for `_test_grouped_gemm_fp8_rowwise`, whose body the reference
+                     keeps as a string (base_testing.py:43-96, the test is switched off there because
+                     FBGEMM's quantize_fp8_row is absent): the string is parsed and its expected-value
+                     loop (:75-88) executed with a stand-in row quantiser (scale = amax/448 per row)
   backward.npz     : `_pytorch_reference_backward` (kernels/MoE/group_GEMM/triton/testing/
                      pytorch_reference_backwards.py:165-197) on three small cases
   quant_1x128.npz  : `_float8_groupwise_quant_kernel` (float8_groupwise_quant.py:20-50)
@@ -32,7 +36,9 @@ import types
 import numpy as np
 import torch
 
-REF = os.environ.get("APPLIED_AI_REFERENCE", "/root/reference")
+REF = os.environ.get("APPLIED_AI_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    sys.exit("set APPLIED_AI_REFERENCE to a checkout of the reference repository")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
@@ -99,6 +105,66 @@ def golden_grouped():
     out["atol"] = np.array(captured["tol"]["atol"])
     np.savez_compressed(os.path.join(HERE, "grouped_bf16.npz"), **out)
     print("grouped_bf16.npz:", len(shapes), "cases, tol", captured["tol"])
+
+
+def golden_fp8_rowwise():
+    """The reference keeps its FP8 row-wise test as a string expression inside the test class
+    (dev/triton_groupGEMM/testing/base_testing.py:43-96).  Parse that string, take
+    `_test_grouped_gemm_fp8_rowwise` out of it and run it on the CPU: the Triton entry point is a
+    recorder, `quantize_fp8_row` (FBGEMM, absent) is a stand-in with the published row-wise
+    recipe (one fp32 scale per row, amax / 448, e4m3 values), and torch.testing.assert_close
+    records the `expected_result` the reference's own loop computed (:75-88) and its tolerances (:90)."""
+    import textwrap
+    path = os.path.join(REF, "dev/triton_groupGEMM/testing/base_testing.py")
+    tree = ast.parse(open(path).read())
+    body = None
+    for node in ast.walk(tree):
+        if (isinstance(node, ast.Expr) and isinstance(node.value, ast.Constant) and isinstance(node.value.value, str)
+                and "_test_grouped_gemm_fp8_rowwise" in node.value.value):
+            body = node.value.value
+    if body is None:
+        raise KeyError("the FP8 row-wise test body was not found in " + path)
+    inner = ast.parse(textwrap.dedent(body))
+    fn_node = next(n for n in ast.walk(inner)
+                   if isinstance(n, ast.FunctionDef) and n.name == "_test_grouped_gemm_fp8_rowwise")
+    captured = {}
+
+    def quantize_fp8_row(t):
+        f = t.float()
+        scale = f.abs().amax(dim=-1).clamp_min(1e-12) / 448.0
+        q = (f / scale[:, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+        return q, scale
+
+    def fake_fp8(a_fp8, b_fp8, m_sizes, a_scale, b_scale):
+        captured.update(a=a_fp8.clone(), b=b_fp8.clone(), m_sizes=m_sizes.clone(), a_scale=a_scale.clone(),
+                        b_scale=b_scale.clone())
+        return torch.zeros(a_fp8.shape[0], b_fp8.shape[0] // m_sizes.numel(), dtype=torch.bfloat16)
+
+    def record(result, expected, **kw):
+        captured["expected"] = expected.clone()
+        captured["tol"] = kw
+
+    from typing import Tuple
+    ns = {"torch": TorchProxy(record), "grouped_gemm_fp8_rowwise": fake_fp8, "quantize_fp8_row": quantize_fp8_row,
+          "self": types.SimpleNamespace(assertTrue=lambda c: None), "Tuple": Tuple}
+    fn = compile_function(fn_node, ns, path)
+    out = {}
+    shapes = [(1, 64, 256, 256), (4, 64, 256, 256), (4, 512, 256, 256), (16, 512, 256, 256)]  # :92-96 uses these
+    torch.manual_seed(0)  # base_testing.py:41
+    for i, shape in enumerate(shapes):
+        fn(shape, torch.device("cpu"))
+        out[f"shape{i}"] = np.array(shape, dtype=np.int32)
+        out[f"a{i}"] = captured["a"].view(torch.uint8).numpy()
+        out[f"b{i}"] = captured["b"].view(torch.uint8).numpy()
+        out[f"a_scale{i}"] = captured["a_scale"].numpy().astype(np.float32)
+        out[f"b_scale{i}"] = captured["b_scale"].numpy().astype(np.float32)
+        out[f"m_sizes{i}"] = captured["m_sizes"].numpy().astype(np.int32)
+        out[f"expected{i}"] = bits16(captured["expected"])
+    out["n_cases"] = np.array(len(shapes))
+    out["rtol"] = np.array(captured["tol"]["rtol"])
+    out["atol"] = np.array(captured["tol"]["atol"])
+    np.savez_compressed(os.path.join(HERE, "grouped_fp8_rowwise.npz"), **out)
+    print("grouped_fp8_rowwise.npz:", len(shapes), "cases, tol", captured["tol"])
 
 
 def golden_torch_moe():
@@ -191,7 +257,11 @@ if __name__ == "__main__":
     if "--only-backward" in sys.argv:
         golden_backward()
         sys.exit(0)
+    if "--only-fp8-rowwise" in sys.argv:
+        golden_fp8_rowwise()
+        sys.exit(0)
     golden_grouped()
+    golden_fp8_rowwise()
     golden_torch_moe()
     golden_align_example()
     golden_quant()

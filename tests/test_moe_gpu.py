@@ -132,3 +132,28 @@ def test_fused_moe_layer_and_inplace():
     assert O.rel_err(out.cpu().float(), ref) <= BF16_REL_TOL
     ret = B.fused_moe(h, w1.to(DEV), w2.to(DEV), tw.to(DEV), ids.to(DEV), inplace=True)
     assert ret.data_ptr() == h.data_ptr() and torch.equal(h, out)
+
+
+def test_full_size_mixtral_layer():
+    """The Mixtral-8x7B FFN layer shapes at full size (T=4096, H=4096, I=14336, E=8, top-2): routing bit-exact
+    on all 8192 routed rows, the layer output on 64 sampled tokens against the reference's `torch_moe`
+    procedure (kernels/triton/inference/col_major_moe_gemm/test_moe_gemm.py:16-30, routing fed as at :54-57)."""
+    T, H, I, E, k = 4096, 4096, 14336, 8, 2
+    tw, ids = C.routing(T, E, k, 1002)
+    gd = torch.Generator(device=DEV).manual_seed(1002)
+    hidden = torch.randn(T, H, generator=gd, device=DEV).to(torch.bfloat16)
+    w1 = torch.empty(E, 2 * I, H, dtype=torch.bfloat16, device=DEV)
+    w2 = torch.empty(E, H, I, dtype=torch.bfloat16, device=DEV)
+    for e in range(E):
+        w1[e] = (torch.randn(2 * I, H, generator=gd, device=DEV) * H ** -0.5).to(torch.bfloat16)
+        w2[e] = (torch.randn(H, I, generator=gd, device=DEV) * I ** -0.5).to(torch.bfloat16)
+    got = B.route(ids.to(DEV), E)
+    for a, b, name in zip(got, O.route_ref(ids, E), ("m_sizes", "offsets", "perm", "inv_perm")):
+        assert torch.equal(a.cpu(), b), name
+    out = B.fused_moe(hidden, w1, w2, tw.to(DEV), ids.to(DEV))
+    assert tuple(out.shape) == (T, H) and bool(torch.isfinite(out.float()).all())
+    pick = torch.randperm(T, generator=torch.Generator().manual_seed(5))[:64]
+    ref = O.torch_moe_ref(hidden[pick.to(DEV)].cpu(), w1.cpu(), w2.cpu(), tw[pick], ids[pick])
+    got_rows = out[pick.to(DEV)].cpu().float()
+    assert O.rel_err(got_rows, ref) <= BF16_REL_TOL
+    assert torch.allclose(got_rows, ref, atol=1e-2 * float(ref.abs().max()), rtol=1.6e-2)

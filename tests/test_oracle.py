@@ -34,6 +34,24 @@ def test_grouped_loop_matches_reference_expected():
             float(y_ng.abs().sum()) - float(y.abs().sum())) < 1e-3 * float(y.abs().sum())
 
 
+def test_fp8_rowwise_loop_matches_reference_expected():
+    """Fixture = the expected values of the reference's own (switched-off) FP8 row-wise test,
+    computed by its loop at dev/triton_groupGEMM/testing/base_testing.py:75-88."""
+    z = load_npz("grouped_fp8_rowwise.npz")
+    for i in range(int(z["n_cases"])):
+        G, M, N, K = [int(v) for v in z[f"shape{i}"]]
+        a = torch.from_numpy(z[f"a{i}"]).view(torch.float8_e4m3fn)
+        b = torch.from_numpy(z[f"b{i}"]).view(torch.float8_e4m3fn)
+        a_s, b_s = torch.from_numpy(z[f"a_scale{i}"]), torch.from_numpy(z[f"b_scale{i}"])
+        m_sizes = torch.from_numpy(z[f"m_sizes{i}"])
+        expected = bf16_from_bits(z[f"expected{i}"]).float()
+        assert a.shape == (M, K) and b.shape == (G * N, K) and int(m_sizes.sum()) == M
+        y = O.grouped_gemm_fp8_rowwise_ref(a, b, m_sizes, a_s, b_s)
+        # the reference stores its fp32 loop result as bf16: one rounding apart, then its own tolerance (:90)
+        assert torch.equal(y.to(torch.bfloat16).float(), expected) or O.rel_err(y, expected) < 4e-3
+        torch.testing.assert_close(y.to(torch.bfloat16).float(), expected, rtol=float(z["rtol"]), atol=float(z["atol"]))
+
+
 def test_torch_moe_matches_reference_output():
     z = load_npz("torch_moe.npz")
     for i in range(int(z["n_cases"])):

@@ -17,6 +17,7 @@ import pytest
 import torch
 
 from applied_ai_b200 import _lib
+from oracle import grouped as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -60,6 +61,9 @@ def test_route_noalloc_matches_route_on_two_calls_in_a_row():
         for a, b, name in zip(got, ref, ("m_sizes", "offsets", "perm", "inv_perm")):
             assert torch.equal(a, b), f"{name} differs for R={R} E={E}"
         assert int(got[0].sum()) == R
+        # and against the CPU restatement of the ordering itself, not only against the sibling entry point
+        for a, b, name in zip(got, O.route_ref(ids.cpu(), E), ("m_sizes", "offsets", "perm", "inv_perm")):
+            assert torch.equal(a.cpu(), b), f"{name} differs from the oracle for R={R} E={E}"
 
 
 def test_route_noalloc_rejects_sizes_beyond_its_array():
