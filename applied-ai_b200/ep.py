@@ -28,9 +28,10 @@ import torch.distributed as dist
 class CudaOps:
     """The layer's compute steps on the GPU.  mode: "bf16" or "fp8_blockwise"."""
 
-    def __init__(self, w1, w2, mode="bf16", cta_group=0, fuse_requant=False):
-        """fuse_requant (fp8_blockwise): quantise the SwiGLU output inside the gate+up GEMM's epilogue
-        instead of with a separate 1x128 quantiser pass."""
+    def __init__(self, w1, w2, mode="bf16", cta_group=0, fuse_requant=True):
+        """fuse_requant (fp8_blockwise, default): the gate+up GEMM's epilogue quantises the fp32 SwiGLU
+        values 1x128 itself (same formula and bytes as float8_groupwise_quantize on those values);
+        False rounds them to bf16 first and runs the separate quantiser pass."""
         from . import groupgemm, moe, quant
         self._gg, self._moe, self._quant = groupgemm, moe, quant
         self.mode = mode
@@ -43,6 +44,21 @@ class CudaOps:
             self.w2, self.w2_scale = self._quantize_weight(w2)
         else:
             raise ValueError("mode must be 'bf16' or 'fp8_blockwise'")
+
+    @classmethod
+    def from_quantized(cls, w1q, w1_scale, w2q, w2_scale, cta_group=0, fuse_requant=True):
+        """fp8_blockwise ops from weights that are already e4m3 with 128x128 block scales
+        (w [E, N, K] float8_e4m3fn, scales [E, ceil(N/128), K/128] fp32), e.g. loaded from a
+        checkpoint or quantised expert by expert to bound the set-up memory."""
+        if w1q.dtype != torch.float8_e4m3fn or w2q.dtype != torch.float8_e4m3fn:
+            raise ValueError("from_quantized takes float8_e4m3fn weights")
+        self = cls.__new__(cls)
+        from . import groupgemm, moe, quant
+        self._gg, self._moe, self._quant = groupgemm, moe, quant
+        self.mode, self.cta_group, self.fuse_requant = "fp8_blockwise", cta_group, bool(fuse_requant)
+        self.w1, self.w1_scale = w1q.contiguous(), w1_scale.contiguous()
+        self.w2, self.w2_scale = w2q.contiguous(), w2_scale.contiguous()
+        return self
 
     def _quantize_weight(self, w):
         if w.dtype == torch.float8_e4m3fn:
