@@ -36,6 +36,8 @@ struct SmemTail {
     uint64_t empty[8];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t out_full;   // block-wise FP8 kernel: the promotion warps have parked a tile's rows for the sending warps
+    uint64_t out_empty;  //   ... the sending warps' copies have read them
     uint32_t tmem_base;
     int abort_flag;
     int invalid;
@@ -296,6 +298,8 @@ __device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GG
             mbar_init(&st->acc_full[b], 1);
             mbar_init(&st->acc_empty[b], acc_empty_count);
         }
+        mbar_init(&st->out_full, 8);   // one arrival per promotion warp
+        mbar_init(&st->out_empty, 2);  // one per sending warp
         mbar_init_fence();
     }
 }

@@ -75,16 +75,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Upper limit on any single wait.  The longest legitimate wait is one tile's
 // main loop (tens of microseconds); this limit only ever ends a protocol error.
 constexpr uint64_t kWaitLimitNs = 400ull * 1000ull * 1000ull;
+#ifndef B200MOE_WAIT_SUSPEND_NS
+#define B200MOE_WAIT_SUSPEND_NS 0
+#endif
+
+// Same probe with a suspend-time hint: the thread may sleep in hardware for up to `hint_ns`
+// and is woken when the phase completes, instead of coming back at once to probe again.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA:
 // once any role gives up, every other role's next check gives up too.
+// SUSPEND_NS > 0: each probe of the loop may sleep that long in hardware (woken by the barrier);
+// a waiting warp then leaves its scheduler's issue slots to the warps that have work.
+template <uint32_t SUSPEND_NS = B200MOE_WAIT_SUSPEND_NS>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if (((++spins) & 0x3F) == 0) {
+    while (!(SUSPEND_NS > 0 ? mbar_try_wait_suspend(bar, parity, SUSPEND_NS) : mbar_try_wait(bar, parity))) {
+        if (SUSPEND_NS > 0 || ((++spins) & 0x3F) == 0) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
