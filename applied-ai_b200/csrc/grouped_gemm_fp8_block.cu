@@ -412,20 +412,33 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     }
                 }
                 uint8_t* const q_row = static_cast<uint8_t*>(p.y) + static_cast<size_t>(cur_row) * p.ldy + col;
+                // f / scale for 64 values that share the divisor: with y = RN(1 / scale), q0 = RN(f * y),
+                // r = f - q0 * scale (exact in an FMA) and q1 = RN(q0 + r * y), q1 is the correctly rounded
+                // quotient (Markstein's correction step) — three instructions per value instead of a full
+                // division.  A divisor whose significand is all ones, where the reciprocal step is not
+                // covered, takes the ordinary division.
+                const float inv_scale = __frcp_rn(scale);
+                if ((__float_as_uint(scale) & 0x007fffffu) != 0x007fffffu) {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        const float q0 = f[j] * inv_scale;
+                        f[j] = fmaf(fmaf(-q0, scale, f[j]), inv_scale, q0);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) f[j] = __fdiv_rn(f[j], scale);
+                }
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     uint32_t w[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        uint32_t packed = 0;
+                        float v[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            float v = __fdiv_rn(f[c4 * 16 + i * 4 + j], scale);
-                            v = fminf(fmaxf(v, -448.0f), 448.0f);
-                            packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3))
-                                      << (8 * j);
-                        }
-                        w[i] = packed;
+                        for (int j = 0; j < 4; ++j) v[j] = fminf(fmaxf(f[c4 * 16 + i * 4 + j], -448.0f), 448.0f);
+                        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0], v[1]), __NV_SATFINITE, __NV_E4M3);
+                        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2], v[3]), __NV_SATFINITE, __NV_E4M3);
+                        w[i] = lo | (hi << 16);
                     }
                     if constexpr (BULK)
                         my_slot[c4] = make_uint4(w[0], w[1], w[2], w[3]);
