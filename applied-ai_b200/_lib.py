@@ -32,6 +32,7 @@ STATUS_NAMES = {
     19: "device-side wait ran out (epilogue)",
     20: "self-test wait ran out (expected)",
     24: "expert-parallel dispatch: a rank would receive more rows than its receive buffer holds",
+    25: "expert-parallel barrier: a peer rank's flag did not arrive within the limit",
     32: "kernel image not built for sm_100a",
 }
 
@@ -50,6 +51,7 @@ SIGNATURES = {
     "b200moe_ep_plan": [_c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp],
     "b200moe_ep_push": [_c_vp, _c_i64, _c_vp, _c_i64, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
                         _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_vp],
+    "b200moe_ep_barrier": [_c_vp, _c_int, _c_int, _c_int, _c_int, ctypes.c_uint64, _c_vp, _c_vp],
     "b200moe_enable_peer_access": [_c_int],
     "b200moe_ipc_export": [_c_vp, _c_vp, ctypes.POINTER(ctypes.c_uint64)],
     "b200moe_ipc_open": [_c_vp, ctypes.POINTER(_c_vp)],
@@ -78,7 +80,7 @@ KERNELS_PER_CALL = {
     "b200moe_grouped_gemm_ex": 1, "b200moe_sm100_gemm_f16": 1, "b200moe_grouped_gemm_backward": 5,
     "b200moe_route": 3, "b200moe_route_noalloc": 3, "b200moe_moe_align_block_size": 5, "b200moe_gather_rows": 1,
     "b200moe_swiglu": 1, "b200moe_combine_topk": 1, "b200moe_quant_1x128": 1, "b200moe_ep_plan": 1,
-    "b200moe_ep_push": 1, "b200moe_selftest_wait_timeout": 1,
+    "b200moe_ep_push": 1, "b200moe_ep_barrier": 1, "b200moe_selftest_wait_timeout": 1,
 }
 _launches = 0
 

@@ -14,6 +14,7 @@ enum : int32_t {
     kStatusTimeoutEpilogue = 19,  // epilogue gave up waiting for a finished accumulator
     kStatusSelfTestTimeout = 20,  // the self-test's deliberately unsatisfied wait ran out (expected)
     kStatusCapacity = 24,         // expert-parallel dispatch: a rank would receive more rows than its buffer holds
+    kStatusPeerTimeout = 25,      // expert-parallel barrier: a peer's flag did not arrive within the limit
     kStatusWrongArch = 32,        // kernel image was not built for sm_100a
 };
 

@@ -16,7 +16,7 @@ static_assert(B200MOE_EBADARG == kErrBadArgument && B200MOE_EALIGN == kErrAlignm
                   B200MOE_ETOOLARGE == kErrTooLarge,
               "public and internal error codes must agree");
 static_assert(B200MOE_SBADSIZES == kStatusBadGroupSizes && B200MOE_STIMEOUT_FIRST == kStatusTimeoutProducer &&
-                  B200MOE_STIMEOUT_LAST == kStatusTimeoutEpilogue && B200MOE_SSELFTEST == kStatusSelfTestTimeout && B200MOE_SCAPACITY == kStatusCapacity && B200MOE_SWRONGARCH == kStatusWrongArch,
+                  B200MOE_STIMEOUT_LAST == kStatusTimeoutEpilogue && B200MOE_SSELFTEST == kStatusSelfTestTimeout && B200MOE_SCAPACITY == kStatusCapacity && B200MOE_SPEERTIMEOUT == kStatusPeerTimeout && B200MOE_SWRONGARCH == kStatusWrongArch,
               "public and internal status codes must agree");
 
 extern "C" {
@@ -177,6 +177,11 @@ int b200moe_ep_push(const void* part0, int64_t row_bytes0, const void* part1, in
                           capacity_rows, tokens, peer_part0, peer_part1,
                           reinterpret_cast<long long* const*>(peer_tags), home_rows, home_row_bytes,
                           static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_ep_barrier(int32_t* const* flag_blocks, int P, int my_rank, int slot, int epoch, uint64_t limit_ns,
+                       int32_t* status, b200moe_stream_t stream) {
+    return ep_barrier_launch(flag_blocks, P, my_rank, slot, epoch, limit_ns, status, static_cast<cudaStream_t>(stream));
 }
 
 int b200moe_enable_peer_access(int peer_device) { return enable_peer_access(peer_device); }

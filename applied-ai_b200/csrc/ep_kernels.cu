@@ -124,6 +124,48 @@ ep_push_kernel(const uint8_t* __restrict__ part0, long long bytes0, const uint8_
     __threadfence_system();  // rows are on their way to other GPUs: order them before the kernel ends
 }
 
+// Barrier between the ranks' streams without a collective: thread p tells rank p "my kernels up to
+// here are done" by storing `epoch` into word [slot][me] of rank p's flag block, then waits until
+// rank p has stored the same epoch (or a later one) into this rank's block.  One block of P threads.
+// Everything this rank enqueued before is complete when this kernel starts (stream order), the
+// release store orders it before the flag for the peer, and the acquire load orders the peer's data
+// before whatever this stream runs next.  The wait is bounded: after limit_ns the thread records
+// kStatusPeerTimeout and returns, nothing is left spinning.
+__global__ void __launch_bounds__(64)
+ep_barrier_kernel(int32_t* const* __restrict__ flag_blocks, int P, int me, int slot, int32_t epoch,
+                  unsigned long long limit_ns, int32_t* status) {
+    const int p = threadIdx.x;
+    if (p >= P) return;
+    __threadfence_system();
+    int32_t* theirs = flag_blocks[p] + slot * P + me;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+    const int32_t* mine = flag_blocks[me] + slot * P + p;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (unsigned spins = 0;; ++spins) {
+        int32_t seen;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if (seen - epoch >= 0) break;  // epochs only grow; the difference also survives a wrap
+        if ((spins & 0x3f) == 0x3f) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (now - t0 > limit_ns) {
+                if (status != nullptr) atomicCAS(status, 0, kStatusPeerTimeout);
+                break;
+            }
+        }
+    }
+}
+
+int ep_barrier_launch(int32_t* const* flag_blocks, int P, int me, int slot, int epoch, unsigned long long limit_ns,
+                      int32_t* status, cudaStream_t stream) {
+    if (flag_blocks == nullptr || P <= 0 || P > 64 || me < 0 || me >= P || slot < 0 || slot > 1 || limit_ns == 0 ||
+        limit_ns > 10ull * 1000 * 1000 * 1000)
+        return kErrBadArgument;
+    ep_barrier_kernel<<<1, 64, 0, stream>>>(flag_blocks, P, me, slot, epoch, limit_ns, status);
+    return static_cast<int>(cudaGetLastError());
+}
+
 int ep_plan_launch(const int32_t* counts, int P, int E, int me, int cap, int32_t* dst_base, int32_t* m_loc,
                    int32_t* status, cudaStream_t stream) {
     if (counts == nullptr || dst_base == nullptr || m_loc == nullptr || P <= 0 || E <= 0 || E % P != 0 || me < 0 ||

@@ -32,6 +32,8 @@ int quant_1x128_launch(const void* x, int x_is_fp32, void* q, float* scales, lon
 // Expert-parallel dispatch over peer memory (ep_kernels.cu).
 int ep_plan_launch(const int32_t* counts, int P, int E, int me, int cap, int32_t* dst_base, int32_t* m_loc,
                    int32_t* status, cudaStream_t stream);
+int ep_barrier_launch(int32_t* const* flag_blocks, int P, int me, int slot, int epoch, unsigned long long limit_ns,
+                      int32_t* status, cudaStream_t stream);
 int ep_push_launch(const void* part0, long long bytes0, const void* part1, long long bytes1, const int32_t* perm,
                    int k, const int32_t* offsets, const int32_t* dst_base, int R, int E, int P, int me, int cap,
                    int tokens, void* const* peer0, void* const* peer1, long long* const* peer_tag, void* home,

@@ -148,16 +148,18 @@ class PeerBuffers:
         self.me = dist.get_rank(group)
         self.cap, self.home_rows, self.H = int(capacity_rows), int(home_rows), int(hidden_size)
         self.part_row_bytes = list(part_row_bytes)
-        sizes = [self.cap * b for b in part_row_bytes] + [self.cap * 8, self.home_rows * self.H * 2]
+        # ... + the flag words of the stream barrier (2 slots x P ranks), last so the other offsets keep their order
+        sizes = [self.cap * b for b in part_row_bytes] + [self.cap * 8, self.home_rows * self.H * 2, 2 * self.P * 4]
         self.offsets, total = [], 0
         for sz in sizes:
             self.offsets.append(total)
             total += (sz + 255) // 256 * 256
         self.arena = torch.zeros(max(total, 1 << 21), dtype=torch.uint8, device=device)
         a = self.arena
-        self.parts = [a[o:o + sz] for o, sz in zip(self.offsets[:-2], sizes[:-2])]
-        self.tags = a[self.offsets[-2]:self.offsets[-2] + sizes[-2]].view(torch.int64)
-        self.y_home = a[self.offsets[-1]:self.offsets[-1] + sizes[-1]].view(torch.bfloat16).view(self.home_rows, self.H)
+        self.parts = [a[o:o + sz] for o, sz in zip(self.offsets[:-3], sizes[:-3])]
+        self.tags = a[self.offsets[-3]:self.offsets[-3] + sizes[-3]].view(torch.int64)
+        self.y_home = a[self.offsets[-2]:self.offsets[-2] + sizes[-2]].view(torch.bfloat16).view(self.home_rows, self.H)
+        self.epoch = 0   # stream-barrier epoch: the same on every rank because every rank makes the same calls
         # export: (handle of the allocation the arena lives in, byte offset of the arena inside it)
         lib = _lib.load()
         hbuf = ctypes.create_string_buffer(64)
@@ -190,6 +192,15 @@ class PeerBuffers:
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
+    def barrier(self, slot, status_word, stream, limit_ns=2_000_000_000):
+        """Orders this rank's stream after every rank's kernels enqueued so far (flag words in the peers'
+        arenas, no collective, no host synchronisation).  Called in the same order on every rank."""
+        from . import _lib
+        if slot == 0:
+            self.epoch += 1
+        _lib.check(_lib.load().b200moe_ep_barrier(self.tables[-1].data_ptr(), self.P, self.me, slot, self.epoch,
+                                                  limit_ns, status_word.data_ptr(), stream), "ep_barrier")
+
     def close(self):
         from . import _lib
         lib = _lib.load()
@@ -220,7 +231,7 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, ops, num_experts, group=None, waves=1, exchange="nccl", max_tokens=None, top_k=None,
-                 hidden_size=None, capacity_factor=1.5):
+                 hidden_size=None, capacity_factor=1.5, barrier="flags"):
         """exchange="nccl": all_to_all_single collectives (rows land in local buffers first).
         exchange="peer": rows are written straight into the owner's memory by the sender's push
         kernel and come home through the down GEMM's store (ordinary stores or non-multicast
@@ -245,6 +256,9 @@ class ExpertParallelMoE:
         self.last_plan = None
         self._remap = None
         self.exchange = exchange
+        if barrier not in ("flags", "nccl"):
+            raise ValueError("barrier must be 'flags' or 'nccl'")
+        self.barrier = barrier   # exchange="peer": how the ranks' streams meet ("nccl": one-element all-reduces)
         self.peer = None
         self.profile = False     # when True, forward() records CUDA-event timings of its phases
         self.timings = []        # [(phase, milliseconds)] of the last profiled forward
@@ -260,8 +274,9 @@ class ExpertParallelMoE:
                                     int(hidden_size))
 
     def _forward_peer(self, hidden, topk_weights, topk_ids):
-        """Dispatch by remote stores, return inside the down GEMM; two stream-ordered
-        collectives (1-element all-reduces) order "rows have landed" on every rank."""
+        """Dispatch by remote stores, return inside the down GEMM; two stream barriers (flag words in
+        the peers' arenas, or one-element all-reduces with barrier="nccl") order "rows have landed"
+        and "results are home" on every rank."""
         import ctypes
 
         from . import _lib
@@ -303,14 +318,14 @@ class ExpertParallelMoE:
                                  pb.tables[len(parts)].data_ptr(), pb.y_home.data_ptr(), 2 * H, stream)
         _lib.check(rc, "ep_push")
         mark("push")
-        dist.all_reduce(pb.sync, group=self.group)          # every rank's rows have landed everywhere
+        self._stream_barrier(0, word, stream)                # every rank's rows have landed everywhere
         mark("barrier 1")
         rows = []
         for buf, nbytes, part in zip(pb.parts, pb.part_row_bytes, parts):
             rows.append(buf.view(part.dtype).view(pb.cap, nbytes // part.element_size()))
         ops.expert_ffn(rows, m_loc, peer=(pb.tags, pb.tables[len(parts) + 1], P, pb.home_rows))
         mark("experts (down GEMM stores home)")
-        dist.all_reduce(pb.sync, group=self.group)          # every result row is home
+        self._stream_barrier(1, word, stream)                # every result row is home
         mark("barrier 2")
         out = ops.combine(pb.y_home[:R], inv_perm, topk_weights, T, k)
         mark("combine")
@@ -318,6 +333,12 @@ class ExpertParallelMoE:
             torch.cuda.synchronize()
             self.timings = [(marks[i][0], marks[i - 1][1].elapsed_time(marks[i][1])) for i in range(1, len(marks))]
         return out
+
+    def _stream_barrier(self, slot, word, stream):
+        if self.barrier == "flags":
+            self.peer.barrier(slot, word, stream)
+        else:
+            dist.all_reduce(self.peer.sync, group=self.group)
 
     def raise_on_status(self):
         """Deferred check of everything this layer has enqueued on the current device so far.  The

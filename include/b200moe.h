@@ -40,6 +40,7 @@ typedef void* b200moe_stream_t;
 #define B200MOE_STIMEOUT_LAST 19
 #define B200MOE_SSELFTEST 20       /* b200moe_selftest_wait_timeout: the unsatisfied wait ran out, as it should */
 #define B200MOE_SCAPACITY 24       /* expert-parallel dispatch: a receive buffer is too small for the routed rows */
+#define B200MOE_SPEERTIMEOUT 25    /* expert-parallel barrier: a peer rank's flag did not arrive within the limit */
 #define B200MOE_SWRONGARCH 32
 
 /* flags of the grouped GEMM entry points */
@@ -156,6 +157,18 @@ int b200moe_ep_push(const void* part0, int64_t row_bytes0, const void* part1, in
                     int P, int my_rank, int capacity_rows, int tokens, void* const* peer_part0,
                     void* const* peer_part1, int64_t* const* peer_tags, void* home_rows, int64_t home_row_bytes,
                     b200moe_stream_t stream);
+/* Barrier between the P ranks' streams through flag words in peer-mapped memory, in place of a
+ * collective (a one-element all-reduce costs tens of microseconds, this a few).  flag_blocks is a DEVICE
+ * array of P pointers, entry r = rank r's flag block of 2*P int32 (zero before first use, mapped into
+ * this process like the other exchange buffers).  Thread p stores `epoch` into word [slot][my_rank] of rank
+ * p's block, then waits until rank p has stored an epoch >= `epoch` into word [slot][p] of this rank's
+ * block.  The caller passes the same, growing epoch on every rank (1, 2, 3, ... per call and slot; two
+ * slots so that the two barriers of a step do not share words).  What this rank enqueued before the call
+ * is complete before its flags are stored; what it enqueues after starts after every peer's flag has
+ * been seen.  The wait gives up after limit_ns (1 .. 1e10): status gets B200MOE_SPEERTIMEOUT and the
+ * kernel returns.  No counterpart in the reference, which has no multi-GPU code. */
+int b200moe_ep_barrier(int32_t* const* flag_blocks, int P, int my_rank, int slot, int epoch, uint64_t limit_ns,
+                       int32_t* status, b200moe_stream_t stream);
 int b200moe_enable_peer_access(int peer_device);
 /* b200moe_ipc_export: the 64-byte IPC handle of the cudaMalloc allocation containing dev_ptr
  * and dev_ptr's byte offset in it.  b200moe_ipc_open: map such an allocation into this

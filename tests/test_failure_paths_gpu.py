@@ -38,3 +38,30 @@ def test_selftest_rejects_unbounded_limits():
     assert lib.b200moe_selftest_wait_timeout(0, status.data_ptr(), None) == -1
     assert lib.b200moe_selftest_wait_timeout(10_000_000_000, status.data_ptr(), None) == -1
     assert lib.b200moe_selftest_wait_timeout(1000, None, None) == -1
+
+
+def test_stream_barrier_gives_up_on_a_peer_that_never_signals():
+    """b200moe_ep_barrier with two 'ranks' whose flag blocks both live on this GPU: rank 0 signals both and
+    finds its own flag, but nobody plays rank 1, so that wait runs into its 50 ms limit, reports status 25
+    and returns.  A second call with the missing flag stored by hand passes at once."""
+    lib = _lib.load()
+    P = 2
+    blocks = [torch.zeros(2 * P, dtype=torch.int32, device="cuda") for _ in range(P)]
+    table = torch.tensor([b.data_ptr() for b in blocks], dtype=torch.int64, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    t0 = time.time()
+    assert lib.b200moe_ep_barrier(table.data_ptr(), P, 0, 0, 1, 50_000_000, status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    dt = time.time() - t0
+    assert int(status.item()) == 25 and 0.04 <= dt < 2.0, (int(status.item()), dt)
+    assert blocks[0].tolist() == [1, 0, 0, 0] and blocks[1].tolist() == [1, 0, 0, 0]   # word [slot 0][rank 0] of both
+    assert "peer" in _lib.describe_status(25)
+    status.zero_()
+    blocks[0][1] = 2                      # "rank 1" has signalled epoch 2 already (a peer may be one step ahead)
+    assert lib.b200moe_ep_barrier(table.data_ptr(), P, 0, 0, 2, 50_000_000, status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    # bad arguments are refused on the host
+    assert lib.b200moe_ep_barrier(table.data_ptr(), P, 2, 0, 1, 50_000_000, status.data_ptr(), stream) == -1
+    assert lib.b200moe_ep_barrier(table.data_ptr(), P, 0, 0, 1, 0, status.data_ptr(), stream) == -1
