@@ -41,6 +41,7 @@ STATUS_NAMES = {
 SIGNATURES = {
     "b200moe_version": [],
     "b200moe_build_id": [],
+    "b200moe_kernel_launches": [],     # returns long long (restype set in load)
     "b200moe_grouped_gemm_bf16": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_i64, _c_i64,
                                   _c_int, _c_int, _c_vp, _c_int, _c_vp, _c_vp],
     "b200moe_grouped_gemm_fp8_rowwise": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
@@ -74,28 +75,11 @@ SIGNATURES = {
     "b200moe_quant_1x128": [_c_vp, _c_int, _c_vp, _c_vp, _c_i64, _c_int, _c_vp],
 }
 
-# Kernels each entry point enqueues (for callers that report how many kernels of this library ran).
-KERNELS_PER_CALL = {
-    "b200moe_grouped_gemm_bf16": 1, "b200moe_grouped_gemm_fp8_rowwise": 1, "b200moe_grouped_gemm_fp8_blockwise": 1,
-    "b200moe_grouped_gemm_ex": 1, "b200moe_sm100_gemm_f16": 1, "b200moe_grouped_gemm_backward": 5,
-    "b200moe_route": 3, "b200moe_route_noalloc": 3, "b200moe_moe_align_block_size": 5, "b200moe_gather_rows": 1,
-    "b200moe_swiglu": 1, "b200moe_combine_topk": 1, "b200moe_quant_1x128": 1, "b200moe_ep_plan": 1,
-    "b200moe_ep_push": 1, "b200moe_ep_barrier": 1, "b200moe_selftest_wait_timeout": 1,
-}
-_launches = 0
-
-
 def launch_count():
-    """Kernels enqueued through this loader so far (sum of KERNELS_PER_CALL over the calls made)."""
-    return _launches
-
-
-def _counted(fn, n):
-    def call(*args):
-        global _launches
-        _launches += n
-        return fn(*args)
-    return call
+    """Kernels this library has enqueued in this process so far (counted inside the library at every
+    launch site: b200moe_kernel_launches)."""
+    lib = load()
+    return int(lib.b200moe_kernel_launches())
 
 
 _lock = threading.Lock()
@@ -145,8 +129,8 @@ def load(build_if_missing=True):
             fn = getattr(lib, name)  # AttributeError here = stale library
             fn.argtypes = argtypes
             fn.restype = _c_int
-            if name in KERNELS_PER_CALL:
-                setattr(lib, name, _counted(fn, KERNELS_PER_CALL[name]))
+        lib.b200moe_kernel_launches.argtypes = []
+        lib.b200moe_kernel_launches.restype = ctypes.c_longlong
         if not custom and lib.b200moe_build_id() != _build.source_id():
             raise ImportError(f"{path} does not carry the id of the sources in {_build.CSRC}; rebuild it")
         _lib = lib

@@ -52,6 +52,7 @@ struct GGParams {
     long long x_col_group_stride;  // group g's K range in x starts at column g * this (0: shared columns)
     int n_out;    // output columns per group (N, or N/2 with SwiGLU)
     int n_tiles;  // column tiles per group
+    int tile_mode;  // which row blocks this launch covers (kTilesAll / kTilesMain / kTilesTails)
 };
 
 struct GGLaunch {
@@ -83,6 +84,10 @@ struct GGLaunch {
     int cta_group;   // 0 auto, 1 or 2
     cudaStream_t stream;
 };
+
+// Kernels this library has enqueued in this process (every launch site calls note_launch right after its launch).
+void note_launch(int n = 1);
+long long launches_so_far();
 
 int grouped_gemm_launch(const GGLaunch& a);
 // Backward pieces (grouped_gemm_dw.cu).

@@ -19,9 +19,17 @@ static_assert(B200MOE_SBADSIZES == kStatusBadGroupSizes && B200MOE_STIMEOUT_FIRS
                   B200MOE_STIMEOUT_LAST == kStatusTimeoutEpilogue && B200MOE_SSELFTEST == kStatusSelfTestTimeout && B200MOE_SCAPACITY == kStatusCapacity && B200MOE_SPEERTIMEOUT == kStatusPeerTimeout && B200MOE_SWRONGARCH == kStatusWrongArch,
               "public and internal status codes must agree");
 
+#include <atomic>
+namespace b200moe {
+static std::atomic<long long> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
+}  // namespace b200moe
+
 extern "C" {
 
 int b200moe_version(void) { return 1; }
+long long b200moe_kernel_launches(void) { return launches_so_far(); }
 
 #ifndef B200MOE_BUILD_ID
 #define B200MOE_BUILD_ID 0

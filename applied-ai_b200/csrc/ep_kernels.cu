@@ -163,6 +163,7 @@ int ep_barrier_launch(int32_t* const* flag_blocks, int P, int me, int slot, int 
         limit_ns > 10ull * 1000 * 1000 * 1000)
         return kErrBadArgument;
     ep_barrier_kernel<<<1, 64, 0, stream>>>(flag_blocks, P, me, slot, epoch, limit_ns, status);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -172,6 +173,7 @@ int ep_plan_launch(const int32_t* counts, int P, int E, int me, int cap, int32_t
         me >= P || cap <= 0 || E > 4096)
         return kErrBadArgument;
     ep_plan_kernel<<<1, 256, sizeof(int32_t) * 2 * E, stream>>>(counts, P, E, E / P, me, cap, dst_base, m_loc, status);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -196,6 +198,7 @@ int ep_push_launch(const void* part0, long long bytes0, const void* part1, long 
                                                reinterpret_cast<uint8_t* const*>(peer0),
                                                reinterpret_cast<uint8_t* const*>(peer1), peer_tag,
                                                static_cast<uint8_t*>(home), home_row_bytes);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -124,16 +124,30 @@ struct TileCoord {
     int g, row0, row_end, n_idx;
 };
 
+// Which row blocks of a group one launch covers.  A ragged group whose last 256-row pair tile would hold
+// at most 128 rows wastes half of that tile's MMAs, so the launcher may run two kernels: the "main" one
+// (CTA pairs, 256-row tiles) leaves such a last block out, and the "tails" one (single CTAs, 128-row tiles)
+// computes just those blocks.  Rows are padded to 128 that way instead of 256.
+constexpr int kTilesAll = 0;    // every row block of the group, ceil(m / tile_rows) tiles
+constexpr int kTilesMain = 1;   // tile_rows = 256: a last block of 1..128 rows is left to the tails kernel
+constexpr int kTilesTails = 2;  // tile_rows = 128: only that left-out block (one tile, or none)
+__host__ __device__ __forceinline__ int group_row_tiles(int m, int tile_rows, int mode) {
+    if (mode == kTilesMain) return (m + 127) / 256;
+    if (mode == kTilesTails) return ((m & 255) >= 1 && (m & 255) <= 128) ? 1 : 0;
+    return (m + tile_rows - 1) / tile_rows;
+}
+__host__ __device__ __forceinline__ int group_first_row(int m, int mode) { return mode == kTilesTails ? (m & ~255) : 0; }
+
 // Maps a global tile number to its group and position.  `g` only moves forward.
 __device__ __forceinline__ TileCoord locate_tile(int t, int& g, const int* tile_off, const int* row_off,
-                                                 int tile_rows) {
+                                                 int tile_rows, int mode = kTilesAll) {
     while (tile_off[g + 1] <= t) ++g;
     const int local = t - tile_off[g];
     const int m_g = row_off[g + 1] - row_off[g];
-    const int tiles_m = (m_g + tile_rows - 1) / tile_rows;
+    const int tiles_m = group_row_tiles(m_g, tile_rows, mode);
     TileCoord c;
     c.g = g;
-    c.row0 = row_off[g] + (local % tiles_m) * tile_rows;
+    c.row0 = row_off[g] + group_first_row(m_g, mode) + (local % tiles_m) * tile_rows;
     c.row_end = row_off[g + 1];
     c.n_idx = local / tiles_m;
     return c;
@@ -264,7 +278,7 @@ __device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GG
             bad = 1;
             m = 0;
         }
-        int tiles = ((m + tile_rows - 1) / tile_rows) * p.n_tiles;
+        int tiles = group_row_tiles(m, tile_rows, p.tile_mode) * p.n_tiles;
         int rs = m, ts = tiles;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -325,7 +339,7 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
     for (int wk = cluster_id; wk < ws.total_work; wk += num_clusters) {
         int t, half;
         decode_work(wk, ws, &t, &half);
-        const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
+        const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows, p.tile_mode);
         const int row0 = tc.row0 + static_cast<int>(cta_rank) * kRowsPerCta;
         int nb0 = SWIGLU ? tc.n_idx * 128 : tc.n_idx * kTileN;
         int nb1 = SWIGLU ? p.n_out + tc.n_idx * 128 : tc.n_idx * kTileN + 128;

@@ -145,7 +145,7 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
         for (int wk = cluster_id; wk < ws.total_work; wk += num_clusters) {
             int t, half;
             decode_work(wk, ws, &t, &half);
-            const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
+            const TileCoord tc = locate_tile(t, g, st->tile_off, st->row_off, kTileRows, p.tile_mode);
             int ok = 1;
             if (lane == 0) ok = mbar_wait(&st->acc_full[buf], acc_phase, abort_flag) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -297,6 +297,7 @@ static int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, cons
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, p);
+    if (e == cudaSuccess) note_launch();
     return static_cast<int>(e);
 }
 
@@ -365,18 +366,29 @@ int grouped_gemm_launch(const GGLaunch& a) {
     p.c_in = a.c_in;
     p.alpha = a.alpha;
     p.beta = a.beta;
-    p.idesc = make_idesc(fp8, 128 * ctas, kTileN, a.is_f16 != 0);
-    p.idesc_half = make_idesc(fp8, 128 * ctas, kTileN / 2, a.is_f16 != 0);
+    // Auto tiling with CTA pairs on ragged groups: two launches, see group_row_tiles().  The pairs' kernel
+    // leaves out a group's last row block when it holds at most 128 rows, a single-CTA launch computes those
+    // blocks as 128-row tiles.  (Group sizes live on the device: the second launch is made in any case
+    // and finds no tiles when no group has such a block.)
+    const bool split_tails = a.cta_group == 0 && ctas == 2 && a.m_sizes != nullptr;
+    auto launch = [&](int nctas, int mode) -> int {
+        p.tile_mode = mode;
+        p.idesc = make_idesc(fp8, 128 * nctas, kTileN, a.is_f16 != 0);
+        p.idesc_half = make_idesc(fp8, 128 * nctas, kTileN / 2, a.is_f16 != 0);
 #define B200MOE_LAUNCH(EB, SC, EP)                                                          \
-    (ctas == 1 ? launch_variant<EB, 1, SC, EP>(tm_x, tm_w, p, di.sms, a.stream)              \
-               : launch_variant<EB, 2, SC, EP>(tm_x, tm_w, p, di.sms, a.stream))
-    if (!fp8 && a.epilogue == 0) return B200MOE_LAUNCH(2, 0, 0);
-    if (!fp8 && a.epilogue == 1) return B200MOE_LAUNCH(2, 0, 1);
-    if (!fp8 && a.epilogue == 2) return B200MOE_LAUNCH(2, 0, 2);
-    if (fp8 && a.scale_mode == 1) return B200MOE_LAUNCH(1, 1, 0);
-    if (fp8 && a.scale_mode == 0 && a.epilogue == 0) return B200MOE_LAUNCH(1, 0, 0);
+    (nctas == 1 ? launch_variant<EB, 1, SC, EP>(tm_x, tm_w, p, di.sms, a.stream)             \
+                : launch_variant<EB, 2, SC, EP>(tm_x, tm_w, p, di.sms, a.stream))
+        if (!fp8 && a.epilogue == 0) return B200MOE_LAUNCH(2, 0, 0);
+        if (!fp8 && a.epilogue == 1) return B200MOE_LAUNCH(2, 0, 1);
+        if (!fp8 && a.epilogue == 2) return B200MOE_LAUNCH(2, 0, 2);
+        if (fp8 && a.scale_mode == 1) return B200MOE_LAUNCH(1, 1, 0);
+        if (fp8 && a.scale_mode == 0 && a.epilogue == 0) return B200MOE_LAUNCH(1, 0, 0);
 #undef B200MOE_LAUNCH
-    return kErrBadArgument;
+        return kErrBadArgument;
+    };
+    if (!split_tails) return launch(ctas, kTilesAll);
+    if (int e = launch(2, kTilesMain)) return e;
+    return launch(1, kTilesTails);
 }
 
 }  // namespace b200moe

@@ -418,7 +418,9 @@ static int launch_dw(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const DWP
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, p));
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, p);
+    if (e == cudaSuccess) note_launch();
+    return static_cast<int>(e);
 }
 
 long long dw_padded_cols(int M, int G) { return ((static_cast<long long>(M) + 63) / 64 + G + 1) * 64; }
@@ -431,6 +433,7 @@ int transpose_pad_launch(const void* src, long long ld, long long col_group_stri
     const dim3 grid(static_cast<unsigned>(mpad / 64), static_cast<unsigned>((C + 63) / 64), 1);
     transpose_pad_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), ld, col_group_stride, C,
                                                    m_sizes, G, M, static_cast<__nv_bfloat16*>(out), mpad);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -440,6 +443,7 @@ int transpose_batched_launch(const void* src, void* dst, int B, int R, int C, cu
                     static_cast<unsigned>(B));
     transpose_batched_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src),
                                                        static_cast<__nv_bfloat16*>(dst), R, C);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -272,7 +272,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         };
         const int wb_delta = kSwiglu ? (p.n_out / 128) * kblocks : 0;
         auto enter_tile = [&](int t) {
-            const TileCoord c = locate_tile(t, g, st->tile_off, st->row_off, kTileRows);
+            const TileCoord c = locate_tile(t, g, st->tile_off, st->row_off, kTileRows, p.tile_mode);
             const int r = c.row0 + static_cast<int>(cta_rank) * kRowsPerCta + quarter * 32 + lane;
             const int blk_a = kSwiglu ? c.n_idx : 2 * c.n_idx + half;
             TileState s;
@@ -589,7 +589,9 @@ static int launch_block_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, p));
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, p);
+    if (e == cudaSuccess) note_launch();
+    return static_cast<int>(e);
 }
 
 #ifdef B200MOE_TRACE
@@ -660,26 +662,35 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     p.c_in = nullptr;
     p.alpha = 1.0f;
     p.beta = 0.0f;
-    p.idesc = make_idesc(true, 128 * ctas, kTileN);
-    p.idesc_half = p.idesc;
     // outputs made of whole, 16-byte aligned runs leave through bulk copies
     const bool bulk = p.n_out % 128 == 0 && a.ldy % 8 == 0 && a.y_col_group_stride % 8 == 0 &&
                       (a.row_tags != nullptr || (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0);
-    if (a.epilogue == 3)  // (its argument checks above already demand aligned, whole 128-column runs)
-        return ctas == 1 ? launch_block_variant<1, 3, true>(tm_x, tm_w, p, di.sms, a.stream)
-                         : launch_block_variant<2, 3, true>(tm_x, tm_w, p, di.sms, a.stream);
-    if (a.epilogue == 0) {
+    // CTA pairs on ragged groups in auto mode: two launches, see group_row_tiles() (a group's last row block
+    // of at most 128 rows goes to a single-CTA launch instead of filling half of a pair tile)
+    const bool split_tails = a.cta_group == 0 && ctas == 2;
+    auto launch = [&](int nctas, int mode) -> int {
+        p.tile_mode = mode;
+        p.idesc = make_idesc(true, 128 * nctas, kTileN);
+        p.idesc_half = p.idesc;
+        if (a.epilogue == 3)  // (its argument checks above already demand aligned, whole 128-column runs)
+            return nctas == 1 ? launch_block_variant<1, 3, true>(tm_x, tm_w, p, di.sms, a.stream)
+                              : launch_block_variant<2, 3, true>(tm_x, tm_w, p, di.sms, a.stream);
+        if (a.epilogue == 0) {
+            if (bulk)
+                return nctas == 1 ? launch_block_variant<1, 0, true>(tm_x, tm_w, p, di.sms, a.stream)
+                                  : launch_block_variant<2, 0, true>(tm_x, tm_w, p, di.sms, a.stream);
+            return nctas == 1 ? launch_block_variant<1, 0>(tm_x, tm_w, p, di.sms, a.stream)
+                              : launch_block_variant<2, 0>(tm_x, tm_w, p, di.sms, a.stream);
+        }
         if (bulk)
-            return ctas == 1 ? launch_block_variant<1, 0, true>(tm_x, tm_w, p, di.sms, a.stream)
-                             : launch_block_variant<2, 0, true>(tm_x, tm_w, p, di.sms, a.stream);
-        return ctas == 1 ? launch_block_variant<1, 0>(tm_x, tm_w, p, di.sms, a.stream)
-                         : launch_block_variant<2, 0>(tm_x, tm_w, p, di.sms, a.stream);
-    }
-    if (bulk)
-        return ctas == 1 ? launch_block_variant<1, 1, true>(tm_x, tm_w, p, di.sms, a.stream)
-                         : launch_block_variant<2, 1, true>(tm_x, tm_w, p, di.sms, a.stream);
-    return ctas == 1 ? launch_block_variant<1, 1>(tm_x, tm_w, p, di.sms, a.stream)
-                     : launch_block_variant<2, 1>(tm_x, tm_w, p, di.sms, a.stream);
+            return nctas == 1 ? launch_block_variant<1, 1, true>(tm_x, tm_w, p, di.sms, a.stream)
+                              : launch_block_variant<2, 1, true>(tm_x, tm_w, p, di.sms, a.stream);
+        return nctas == 1 ? launch_block_variant<1, 1>(tm_x, tm_w, p, di.sms, a.stream)
+                          : launch_block_variant<2, 1>(tm_x, tm_w, p, di.sms, a.stream);
+    };
+    if (!split_tails) return launch(ctas, kTilesAll);
+    if (int e = launch(2, kTilesMain)) return e;
+    return launch(1, kTilesTails);
 }
 
 }  // namespace b200moe

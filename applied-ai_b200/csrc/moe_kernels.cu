@@ -169,9 +169,12 @@ int route_launch(const int32_t* ids, int R, int E, int32_t* m_sizes, int32_t* of
     const int blocks = (num_chunks + kRouteWarps - 1) / kRouteWarps;
     route_count_kernel<<<blocks, kRouteWarps * 32, sizeof(int32_t) * kRouteWarps * E, stream>>>(
         ids, R, E, chunk_len, num_chunks, counts, status);
+    note_launch();
     route_scan_kernel<<<(E + 7) / 8, 256, 0, stream>>>(counts, E, num_chunks, m_sizes);
+    note_launch();
     route_scatter_kernel<<<blocks, kRouteWarps * 32, sizeof(int32_t) * (kRouteWarps + 1) * E, stream>>>(
         ids, R, E, chunk_len, num_chunks, counts, m_sizes, offsets, perm, inv_perm);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -241,10 +244,12 @@ int align_blocks_launch(const int32_t* ids, int R, int E, int block_size, int32_
     const long long n_sorted = static_cast<long long>(R) + static_cast<long long>(E) * (block_size - 1);
     fill_i32_kernel<<<static_cast<int>(std::min<long long>((n_sorted + 255) / 256, 1184)), 256, 0, stream>>>(
         sorted_ids, n_sorted, R);
+    note_launch();
     const int blocks = std::max(1, std::min((R + 255) / 256, 592));
     align_blocks_kernel<<<blocks, 256, sizeof(int32_t) * (E + 1), stream>>>(m_sizes, offsets, perm, R, E, block_size,
                                                                              sorted_ids, expert_ids,
                                                                              num_tokens_post_pad);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -338,6 +343,7 @@ int gather_rows_launch(const void* src, const int32_t* idx, int div, void* dst, 
     if (blocks > 148 * 8) blocks = 148 * 8;
     gather_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(src), idx, div,
                                                    static_cast<uint8_t*>(dst), rows, row_bytes, src_rows, vec_ok);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -376,6 +382,7 @@ int swiglu_launch(const void* in, void* out, long long rows, int d, cudaStream_t
     if (blocks > 148 * 16) blocks = 148 * 16;
     swiglu_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in),
                                                                 static_cast<__nv_bfloat16*>(out), rows, d);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -440,6 +447,7 @@ int combine_topk_launch(const void* y, const int32_t* inv_perm, const float* wei
     if (blocks > 148 * 16) blocks = 148 * 16;
     combine_topk_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(y), inv_perm, weight, static_cast<__nv_bfloat16*>(out), T, k, H, y_rows);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -509,12 +517,15 @@ int quant_1x128_launch(const void* x, int x_is_fp32, void* q, float* scales, lon
     if (groups == 0) return 0;
     long long blocks = (groups + 15) / 16;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (x_is_fp32)
+    if (x_is_fp32) {
         quant_1x128_kernel<float><<<static_cast<int>(blocks), 256, 0, stream>>>(
             static_cast<const float*>(x), static_cast<uint8_t*>(q), scales, groups);
-    else
+        note_launch();
+    } else {
         quant_1x128_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(
             static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scales, groups);
+        note_launch();
+    }
     return static_cast<int>(cudaGetLastError());
 }
 

@@ -30,6 +30,7 @@ __global__ void selftest_wait_kernel(uint64_t limit_ns, int32_t* status) {
 int selftest_wait_launch(uint64_t limit_ns, int32_t* status, cudaStream_t stream) {
     if (status == nullptr || limit_ns == 0 || limit_ns > 2000000000ull) return kErrBadArgument;
     selftest_wait_kernel<<<1, 64, 0, stream>>>(limit_ns, status);
+    note_launch();
     return static_cast<int>(cudaGetLastError());
 }
 

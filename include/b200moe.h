@@ -55,6 +55,10 @@ int b200moe_version(void);
  * The Python loader compares it with the sources on disk and refuses a library that does
  * not match them.  No counterpart in the reference (its kernels are compiled on first use). */
 int b200moe_build_id(void);
+/* How many kernels this library has enqueued in this process so far (all devices, all streams).
+ * For callers that report their launch counts; a grouped GEMM may be one or two kernels.
+ * No counterpart in the reference. */
+long long b200moe_kernel_launches(void);
 
 /* y[rows of group g, g*y_col_group_stride + (0..N)] = x[rows of group g, :] @ w[g]^T
  * x [M,K] bf16 row-major, w [G,N,K] bf16 row-major, m_sizes [G] int32 (device; zeros

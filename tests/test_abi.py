@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def declared_symbols():
     text = open(os.path.join(ROOT, "include", "b200moe.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\bint\s+(b200moe_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(?:int|long long)\s+(b200moe_\w+)\s*\(", text)))
 
 
 def test_library_builds_and_exports_every_declared_symbol():
