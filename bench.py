@@ -701,7 +701,7 @@ def measure_layer(name, exchange, ops, rank, world, dev, args, steps, parity_tok
 
 
 def ep_layer_section(rank, world, dev, args):
-    """The expert-parallel DeepSeek-V3 layer (BASELINE config 4) on the GPUs of this run, both exchanges."""
+    """The expert-parallel DeepSeek-V3 layer on the GPUs of this run, both exchanges."""
     ops = build_layer_ops("c4", rank, world, dev, args.cta_group, args.fuse_requant)
     steps = args.steps
     if world == 1:
