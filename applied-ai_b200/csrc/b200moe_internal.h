@@ -72,6 +72,7 @@ struct GGLaunch {
     const float* c_in;
     float alpha, beta;
     int is_f16;      // 2-byte operands are IEEE half instead of bf16
+    int w_mn_major;  // w is [G, K, N] (N contiguous) instead of [G, N, K]; 16-bit operands, plain epilogue only
     int y_rows;
     long long ldy;
     long long y_col_group_stride;
@@ -90,13 +91,12 @@ void note_launch(int n = 1);
 long long launches_so_far();
 
 int grouped_gemm_launch(const GGLaunch& a);
-// Backward pieces (grouped_gemm_dw.cu).
-long long dw_padded_cols(int M, int G);
-int transpose_pad_launch(const void* src, long long ld, long long col_group_stride, int C, const int32_t* m_sizes,
-                         int G, int M, void* out, long long mpad, cudaStream_t stream);
-int transpose_batched_launch(const void* src, void* dst, int B, int R, int C, cudaStream_t stream);
-int grouped_gemm_dw_launch(const void* dyt, const void* xt, const int32_t* m_sizes, void* dw, int M, int N, int K,
-                           int G, long long mpad, int cta_group, int32_t* status, cudaStream_t stream);
+// Weight gradient (grouped_gemm_dw.cu): dY [M, dy_ld] and x [M, K] are read in place; tail_ws holds the
+// zero-padded copies of the groups' partial last 64-row blocks (dw_workspace_bytes).
+size_t dw_workspace_bytes(int N, int K, int G);
+int grouped_gemm_dw_launch(const void* dy, long long dy_ld, long long dy_col_group_stride, const void* x,
+                           const int32_t* m_sizes, void* dw, int M, int N, int K, int G, void* tail_ws,
+                           int cta_group, int32_t* status, cudaStream_t stream);
 int selftest_wait_launch(uint64_t limit_ns, int32_t* status, cudaStream_t stream);
 // FP8 with 1x128 activation scales [M, K/128] and 128x128 weight scales [G, ceil(N/128), K/128].
 int grouped_gemm_fp8_block_launch(const GGLaunch& a);

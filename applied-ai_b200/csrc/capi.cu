@@ -230,8 +230,7 @@ int b200moe_sm100_gemm_f16(const void* A, const void* B, const void* C, void* D,
 
 int b200moe_backward_workspace_bytes(int M, int N, int K, int G, size_t* bytes) {
     if (bytes == nullptr || M < 0 || N <= 0 || K <= 0 || G <= 0) return kErrBadArgument;
-    const size_t mpad = static_cast<size_t>(dw_padded_cols(M, G));
-    *bytes = 2 * (static_cast<size_t>(G) * K * N + (static_cast<size_t>(N) + K) * mpad) + 512;
+    *bytes = dw_workspace_bytes(N, K, G) + 256;
     return 0;
 }
 
@@ -244,21 +243,17 @@ int b200moe_grouped_gemm_backward(const void* grad_y, const void* x, const void*
     if (grad_y == nullptr || x == nullptr || w == nullptr || m_sizes == nullptr || grad_x == nullptr ||
         grad_w == nullptr || workspace == nullptr || grad_y_ld < N || grad_y_col_group_stride < 0)
         return kErrBadArgument;
+    // every operand is read in place by TMA: 16-byte row pitches
+    if (N % 8 != 0 || K % 8 != 0 || grad_y_ld % 8 != 0 || grad_y_col_group_stride % 8 != 0) return kErrAlignment;
     if (workspace_bytes < need) return kErrTooLarge;
     if (M == 0) return 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const long long mpad = dw_padded_cols(M, G);
-    // workspace: w^T [G, K, N] | grad_y^T [N, mpad] | x^T [K, mpad], each 256-byte aligned
-    auto align = [](uintptr_t p) { return (p + 255) & ~static_cast<uintptr_t>(255); };
-    uintptr_t base = align(reinterpret_cast<uintptr_t>(workspace));
-    void* wt = reinterpret_cast<void*>(base);
-    void* dyt = reinterpret_cast<void*>(align(base + 2ull * G * K * N));
-    void* xt = reinterpret_cast<void*>(align(reinterpret_cast<uintptr_t>(dyt) + 2ull * N * mpad));
-    // grad_x[rows of g] = grad_y[rows of g, block g] @ w[g]: the forward kernel on (grad_y, w^T)
-    if (int e = transpose_batched_launch(w, wt, G, N, K, s)) return e;
+    // grad_x[rows of g] = grad_y[rows of g, block g] @ w[g]: the forward kernel with w[g] [N, K] read as an
+    // MN-major operand (the contraction walks its rows)
     GGLaunch a{};
     a.x = grad_y;
-    a.w = wt;
+    a.w = w;
+    a.w_mn_major = 1;
     a.m_sizes = m_sizes;
     a.y = grad_x;
     a.status = status;
@@ -274,10 +269,9 @@ int b200moe_grouped_gemm_backward(const void* grad_y, const void* x, const void*
     a.stream = s;
     if (int e = grouped_gemm_launch(a)) return e;
     // grad_w[g] = grad_y[rows of g, block g]^T @ x[rows of g]
-    if (int e = transpose_pad_launch(grad_y, grad_y_ld, grad_y_col_group_stride, N, m_sizes, G, M, dyt, mpad, s))
-        return e;
-    if (int e = transpose_pad_launch(x, K, 0, K, m_sizes, G, M, xt, mpad, s)) return e;
-    return grouped_gemm_dw_launch(dyt, xt, m_sizes, grad_w, M, N, K, G, mpad, cta_group, status, s);
+    const uintptr_t tail_ws = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~static_cast<uintptr_t>(255);
+    return grouped_gemm_dw_launch(grad_y, grad_y_ld, grad_y_col_group_stride, x, m_sizes, grad_w, M, N, K, G,
+                                  reinterpret_cast<void*>(tail_ws), cta_group, status, s);
 }
 
 int b200moe_selftest_wait_timeout(uint64_t limit_ns, int32_t* status, b200moe_stream_t stream) {

@@ -321,7 +321,13 @@ __device__ __forceinline__ void build_tables_and_barriers(SmemTail* st, const GG
 // TMA producer, run by ONE thread per CTA: for every tile of this cluster and every
 // 128-byte slice of K, wait for a free stage and fetch this CTA's 128 rows of x and its
 // share of the tile's two 128-row boxes of w[g] (rows nb0.. and nb1..).
-template <int CTAS, int LESS, bool SWIGLU, bool HALF = false>
+//
+// B_MN (16-bit operands only): w is [G, K, N] with N contiguous (an MN-major B operand, see
+// make_sw128_mnmajor_desc).  The CTA's share of the tile's columns then arrives as boxes of 64 contraction
+// rows x 64 columns, 8192 bytes each, one after another: columns c0.., c0+64.. (and two more when one CTA
+// holds all 256 columns).  A half tile uses the first box of each CTA only; the second is fetched all the
+// same so that every stage carries the same byte count.
+template <int CTAS, int LESS, bool SWIGLU, bool HALF = false, bool B_MN = false>
 __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUtensorMap* tm_w, SmemTail* st,
                                               uint32_t ring_addr, const GGParams& p, uint32_t cta_rank,
                                               int cluster_id, int num_clusters, int elems_per_stage, int num_kb) {
@@ -349,6 +355,8 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
             nb0 = SWIGLU ? tc.n_idx * 128 + half * 64 : tc.n_idx * kTileN + half * 128;
             nb1 = SWIGLU ? p.n_out + tc.n_idx * 128 + half * 64 : tc.n_idx * kTileN + half * 128 + 64;
         }
+        // B_MN: first column of this CTA's share (nb0 / nb1 above are exactly that for both tile kinds)
+        const int mn_c0 = (CTAS == 1 || cta_rank == 0) ? nb0 : nb1;
         for (int kb = 0; kb < num_kb; ++kb) {
             if (!__all_sync(0xffffffffu, mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag))) {
                 report(p.status, kStatusTimeoutProducer);
@@ -363,8 +371,13 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
                 if (leader) {
                     mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
                     tma_load_2d(tm_x, bar, a_dst, kx, row0);
-                    tma_load_3d(tm_w, bar, b_dst, k0, nb0, tc.g);
-                    tma_load_3d(tm_w, bar, b_dst + kSubBoxBytes, k0, nb1, tc.g);
+                    if constexpr (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) tma_load_3d(tm_w, bar, b_dst + j * 8192, mn_c0 + j * 64, k0, tc.g);
+                    } else {
+                        tma_load_3d(tm_w, bar, b_dst, k0, nb0, tc.g);
+                        tma_load_3d(tm_w, bar, b_dst + kSubBoxBytes, k0, nb1, tc.g);
+                    }
                 }
             } else {
                 // Bytes of both CTAs are counted on the leader's barrier.
@@ -372,7 +385,12 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tm_x, const CUt
                 if (leader) {
                     if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
                     tma_load_2d_pair(tm_x, bar, a_dst, kx, row0);
-                    tma_load_3d_pair(tm_w, bar, b_dst, k0, cta_rank == 0 ? nb0 : nb1, tc.g);
+                    if constexpr (B_MN) {
+                        tma_load_3d_pair(tm_w, bar, b_dst, mn_c0, k0, tc.g);
+                        tma_load_3d_pair(tm_w, bar, b_dst + 8192, mn_c0 + 64, k0, tc.g);
+                    } else {
+                        tma_load_3d_pair(tm_w, bar, b_dst, k0, cta_rank == 0 ? nb0 : nb1, tc.g);
+                    }
                 }
             }
             __syncwarp();
@@ -435,6 +453,22 @@ inline int encode_w_map(CUtensorMap* m, const void* w, int G, int rows_per_group
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(m, elem_bytes == 2 ? (is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)
                                      : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                     const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
+}
+
+// w viewed as [G, K rows, N] with N contiguous (16-bit elements); box = 64 rows x 64 columns (128 bytes),
+// 128-byte swizzle: the MN-major B operand of producer_loop<..., B_MN = true>.
+inline int encode_w_mn_map(CUtensorMap* m, const void* w, int G, int K, int N, bool is_f16 = false) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return kErrNoDriverEntry;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(G)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(N) * 2, static_cast<cuuint64_t>(N) * 2 * K};
+    cuuint32_t box[3] = {64, 64, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(m, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                      const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -34,7 +34,9 @@ constexpr int kEpiWarps = 4;
 // EPI: 0 plain, 1 SwiGLU (w[g] = [gate rows 0..I) ; up rows I..2I), output has I columns),
 //      2 fp32 output alpha*acc + beta*C (the dense D = alpha*A*B^T + beta*C of
 //        kernels/blackwell/cute_gemm_02_tma/sm100_gemm.cu:157-173).
-template <int ELEM_BYTES, int CTAS, int SCALE, int EPI>
+// B_MN: w is [G, K, N] with N contiguous instead of [G, N, K] (y = x @ w[g] without a transpose: the input
+//      gradient of the layer reads the forward weights as they lie).  16-bit operands only.
+template <int ELEM_BYTES, int CTAS, int SCALE, int EPI, bool B_MN = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GGParams p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
@@ -83,8 +85,8 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 
     if (warp == 0) {
         // ================= TMA producer (the warp walks the loop, one elected lane issues)
-        producer_loop<CTAS, 0, EPI == 1, true>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id, num_clusters,
-                                          kElemsPerStage, num_kb);
+        producer_loop<CTAS, 0, EPI == 1, true, B_MN>(&tm_x, &tm_w, st, ring_addr, p, cta_rank, cluster_id,
+                                                     num_clusters, kElemsPerStage, num_kb);
     } else if (warp == 1) {
         // ================= MMA issuer (leader CTA; the warp walks the loop, one elected lane issues)
         if (cta_rank == 0) {
@@ -111,12 +113,15 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
                     tc_fence_after();
                     const uint32_t a_addr = ring_addr + stage * Cfg::kStageBytes;
                     const uint64_t a_desc = make_sw128_kmajor_desc(a_addr);
-                    const uint64_t b_desc = make_sw128_kmajor_desc(a_addr + kABytes);
+                    const uint64_t b_desc =
+                        B_MN ? make_sw128_mnmajor_desc(a_addr + kABytes) : make_sw128_kmajor_desc(a_addr + kABytes);
+                    // per MMA: 32 bytes along K of a K-major tile (+2 in the descriptor's 16-byte units),
+                    // 16 rows of 128 bytes of an MN-major one (+128)
+                    constexpr uint32_t kBStep = B_MN ? 128u : 2u;
                     if (leader) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            // 32 bytes along K per MMA: +2 in the descriptor's 16-byte units.
-                            umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                            umma<CTAS, kFp8>(d_tmem, a_desc + 2u * k, b_desc + kBStep * k, idesc,
                                              (kb > 0 || k > 0) ? 1u : 0u);
                         }
                         umma_commit<CTAS>(&st->empty[stage]);
@@ -271,10 +276,11 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
 
 // ------------------------------------------------------------------ host side
 
-template <int ELEM_BYTES, int CTAS, int SCALE, int EPI>
+template <int ELEM_BYTES, int CTAS, int SCALE, int EPI, bool B_MN = false>
 static int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const GGParams& p, int sms,
                           cudaStream_t stream) {
-    auto kernel = gg_kernel<ELEM_BYTES, CTAS, SCALE, EPI>;
+    static_assert(!B_MN || ELEM_BYTES == 2, "MN-major operands exist for 16-bit types only");
+    auto kernel = gg_kernel<ELEM_BYTES, CTAS, SCALE, EPI, B_MN>;
     constexpr size_t smem = gg_smem_bytes<CTAS, 0, kEpiWarps * kWarpStageBytes>();
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -320,6 +326,8 @@ int grouped_gemm_launch(const GGLaunch& a) {
     if (a.epilogue < 0 || a.epilogue > 2) return kErrBadArgument;
     if (a.row_tags != nullptr && (a.peer_y == nullptr || a.n_peers <= 0 || a.y_rows <= 0)) return kErrBadArgument;
     if (a.epilogue == 1 && a.scale_mode != 0) return kErrBadArgument;
+    if (a.w_mn_major && (a.elem_bytes != 2 || a.epilogue != 0 || a.scale_mode != 0)) return kErrBadArgument;
+    if (a.w_mn_major && (static_cast<long long>(a.N) * 2) % 16 != 0) return kErrAlignment;  // TMA row pitch of w
     if (a.M == 0) return 0;
 
     DeviceInfo di;
@@ -331,7 +339,11 @@ int grouped_gemm_launch(const GGLaunch& a) {
     const long long x_ld = a.x_ld > 0 ? a.x_ld : a.K;
     if ((x_ld * a.elem_bytes) % 16 != 0 || x_ld > 0x7fffffffll) return kErrAlignment;
     if (int e = encode_x_map(&tm_x, a.x, a.M, static_cast<int>(x_ld), a.elem_bytes, a.is_f16 != 0)) return e;
-    if (int e = encode_w_map(&tm_w, a.w, a.G, a.N, a.K, a.elem_bytes, a.is_f16 != 0)) return e;
+    if (a.w_mn_major) {
+        if (int e = encode_w_mn_map(&tm_w, a.w, a.G, a.K, a.N, a.is_f16 != 0)) return e;
+    } else if (int e = encode_w_map(&tm_w, a.w, a.G, a.N, a.K, a.elem_bytes, a.is_f16 != 0)) {
+        return e;
+    }
 
     GGParams p;
     p.m_sizes = a.m_sizes;
@@ -375,8 +387,11 @@ int grouped_gemm_launch(const GGLaunch& a) {
     const bool split_tails = false;
     auto launch = [&](int nctas, int mode) -> int {
         p.tile_mode = mode;
-        p.idesc = make_idesc(fp8, 128 * nctas, kTileN, a.is_f16 != 0);
-        p.idesc_half = make_idesc(fp8, 128 * nctas, kTileN / 2, a.is_f16 != 0);
+        p.idesc = make_idesc(fp8, 128 * nctas, kTileN, a.is_f16 != 0, a.w_mn_major != 0);
+        p.idesc_half = make_idesc(fp8, 128 * nctas, kTileN / 2, a.is_f16 != 0, a.w_mn_major != 0);
+        if (a.w_mn_major)
+            return nctas == 1 ? launch_variant<2, 1, 0, 0, true>(tm_x, tm_w, p, di.sms, a.stream)
+                              : launch_variant<2, 2, 0, 0, true>(tm_x, tm_w, p, di.sms, a.stream);
 #define B200MOE_LAUNCH(EB, SC, EP)                                                          \
     (nctas == 1 ? launch_variant<EB, 1, SC, EP>(tm_x, tm_w, p, di.sms, a.stream)             \
                 : launch_variant<EB, 2, SC, EP>(tm_x, tm_w, p, di.sms, a.stream))

@@ -2,14 +2,17 @@
 // the second half of grouped_gemm_backward (kernels/MoE/group_GEMM/triton/tgroup_gemm_backwards.py:382;
 // per-group definition in testing/pytorch_reference_backwards.py:165-197).
 //
-// The contraction runs over the ragged row dimension m_g, so both operands are first brought
-// into "rows contiguous" form by transpose_pad_kernel (below): dYT [N, Mpad] and XT [K, Mpad],
-// where every group's columns start at a multiple of 64 and are zero-padded to a multiple of
-// 64, and one extra block of 64 zero columns stands in for empty groups.  After that the
-// problem has the forward kernel's shape — D[n, k] += A[n, m] * B[k, m]^T with both operands
-// K-major — and uses the same TMA ring, tcgen05 pipeline and CTA-pair tiles; only the tile
-// walk differs: every group owns the same number of (n, k) tiles and the K loop length is the
-// group's padded row count / 64.
+// The contraction runs over the ragged row dimension m_g.  dY and X are read where they lie, as MN-major
+// operands (make_sw128_mnmajor_desc: the operand's own dimension, n or k, is the contiguous one, the
+// contraction index m walks the rows), 64 rows of the group per stage, so nothing is transposed.  A group's
+// last block may be partial; its rows would run into the next group, so tail_pack_kernel first copies every
+// group's partial last block (fewer than 64 rows) into a zero-padded 64-row block of a small side buffer
+// ([G*64, N] and [G*64, K]; an empty group gets an all-zero block, which makes its dW zero), and the producer
+// fetches that one block from the side buffer.  Nothing else is copied.
+//
+// The kernel uses the forward kernel's TMA ring, tcgen05 pipeline and CTA-pair tiles; only the tile walk
+// differs: every group owns the same number of (n, k) tiles and the K loop length is the group's row count / 64,
+// rounded up (1 for an empty group).
 #include "gg_common.cuh"
 
 namespace b200moe {
@@ -24,17 +27,15 @@ struct DWParams {
     int M, N, K, G;     // M = rows of x / dY; N, K = weight dims
     int tiles_n, tiles_k;
     uint32_t idesc;
+    long long dy_col_group_stride;  // first column of group g's block of dY = g * this
 };
 
-// Padded column layout shared by the transpose kernel and the dW kernel.
-// koff[g] = first padded column of group g, kcnt[g] = 64-column blocks to contract
-// (empty groups contract the one all-zero block that follows the last group).
-// Optional outputs: pstart[g] = padded start of every group in order (empty groups have
-// pstart[g] == pstart[g+1]; pstart[G] = total), row_off[g] = first real row of the group.
-__device__ __forceinline__ void build_padded_layout(const int32_t* m_sizes, int G, int M, int lane, int* koff,
-                                                    int* kcnt, int* total_blocks, int* bad_out,
-                                                    int* pstart = nullptr, int* row_off = nullptr) {
-    int carry = 0, rows = 0, bad = 0;
+// Run by one warp: row_off[g] = first row of group g (row_off[G] = rows in all groups), kcnt[g] = 64-row
+// blocks to contract (1 for an empty group: the all-zero block of the side buffer); *bad_out is set when a
+// size is negative or the sizes add up to more than M.
+__device__ __forceinline__ void build_row_layout(const int32_t* m_sizes, int G, int M, int lane, int* row_off,
+                                                 int* kcnt, int* bad_out) {
+    int rows = 0, bad = 0;
     for (int base = 0; base < G; base += 32) {
         const int g = base + lane;
         int m = g < G ? m_sizes[g] : 0;
@@ -42,132 +43,25 @@ __device__ __forceinline__ void build_padded_layout(const int32_t* m_sizes, int 
             bad = 1;
             m = 0;
         }
-        const int blocks = (m + 63) >> 6;
-        int bs = blocks, rs = m;
+        int rs = m;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            const int b2 = __shfl_up_sync(0xffffffffu, bs, d);
             const int r2 = __shfl_up_sync(0xffffffffu, rs, d);
-            if (lane >= d) {
-                bs += b2;
-                rs += r2;
-            }
+            if (lane >= d) rs += r2;
         }
         if (g < G) {
-            koff[g] = (carry + bs - blocks) << 6;
-            kcnt[g] = blocks;
-            if (pstart != nullptr) pstart[g] = (carry + bs - blocks) << 6;
-            if (row_off != nullptr) row_off[g] = rows + rs - m;
+            row_off[g] = rows + rs - m;
+            kcnt[g] = m == 0 ? 1 : (m + 63) >> 6;
         }
-        carry += __shfl_sync(0xffffffffu, bs, 31);
         rows += __shfl_sync(0xffffffffu, rs, 31);
         if (rows > M) bad = 1;
     }
     bad = __any_sync(0xffffffffu, bad);
-    __syncwarp();
-    for (int g = lane; g < G; g += 32)
-        if (kcnt[g] == 0) {  // empty group: contract the zero block
-            koff[g] = carry << 6;
-            kcnt[g] = 1;
-        }
     if (lane == 0) {
-        *total_blocks = carry;
+        row_off[G] = rows;
         *bad_out = bad;
-        if (pstart != nullptr) pstart[G] = carry << 6;
-        if (row_off != nullptr) row_off[G] = rows;
     }
-}
-
-// One 64x64 bf16 tile through shared memory, run by 256 threads.
-// Reads src[r][c] for r < rows_in, c < cols_in (zeros elsewhere) with 16-byte loads when the
-// tile is whole and aligned, writes dst[c][r] for c < rows_out, r < cols_out the same way.
-__device__ __forceinline__ void transpose_tile_64(const __nv_bfloat16* src, long long src_ld, int rows_in, int cols_in,
-                                                  __nv_bfloat16* dst, long long dst_ld, int rows_out, int cols_out,
-                                                  __nv_bfloat16 (*tile)[66]) {
-    const bool vec_in = rows_in > 0 && cols_in == 64 && (src_ld % 8) == 0 &&
-                        (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
-    if (vec_in) {
-        for (int idx = threadIdx.x; idx < 64 * 8; idx += blockDim.x) {
-            const int r = idx >> 3, v = idx & 7;
-            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-            if (r < rows_in) raw = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * src_ld) + v);
-            const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
-            uint32_t* t = reinterpret_cast<uint32_t*>(&tile[r][v * 8]);  // rows are 132 bytes apart: 4-byte aligned
-            t[0] = w[0]; t[1] = w[1]; t[2] = w[2]; t[3] = w[3];
-        }
-    } else {
-        for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x) {
-            const int r = idx >> 6, c = idx & 63;
-            tile[r][c] = (r < rows_in && c < cols_in) ? src[static_cast<size_t>(r) * src_ld + c] : __float2bfloat16(0.0f);
-        }
-    }
-    __syncthreads();
-    const bool vec_out = cols_out == 64 && (dst_ld % 8) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
-    if (vec_out) {
-        for (int idx = threadIdx.x; idx < 64 * 8; idx += blockDim.x) {
-            const int c = idx >> 3, v = idx & 7;  // output row c, 8 consecutive output columns r = 8v..8v+7
-            if (c >= rows_out) continue;
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const unsigned short lo = *reinterpret_cast<const unsigned short*>(&tile[v * 8 + 2 * j][c]);
-                const unsigned short hi = *reinterpret_cast<const unsigned short*>(&tile[v * 8 + 2 * j + 1][c]);
-                w[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-            }
-            reinterpret_cast<uint4*>(dst + static_cast<size_t>(c) * dst_ld)[v] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-    } else {
-        for (int idx = threadIdx.x; idx < 64 * 64; idx += blockDim.x) {
-            const int c = idx >> 6, r = idx & 63;
-            if (c < rows_out && r < cols_out) dst[static_cast<size_t>(c) * dst_ld + r] = tile[r][c];
-        }
-    }
-}
-
-// out[c, koff_g + i] = src[off_g + i, col0_g + c]  (i < m_g), zeros in the padding and in the
-// extra zero block.  src has `ld` elements per row; col0_g = g * col_group_stride.
-// grid: x = padded 64-column blocks (upper bound M/64 + G + 1), y = C / 64 (rounded up).
-__global__ void __launch_bounds__(256)
-transpose_pad_kernel(const __nv_bfloat16* __restrict__ src, long long ld, long long col_group_stride, int C,
-                     const int32_t* __restrict__ m_sizes, int G, int M, __nv_bfloat16* __restrict__ out,
-                     long long mpad) {
-    __shared__ int koff[kMaxGroups + 1], kcnt[kMaxGroups + 1], pstart[kMaxGroups + 1], row_off[kMaxGroups + 1];
-    __shared__ int total_blocks, bad;
-    __shared__ __nv_bfloat16 tile[64][66];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp == 0) build_padded_layout(m_sizes, G, M, lane, koff, kcnt, &total_blocks, &bad, pstart, row_off);
-    __syncthreads();
-    if (bad) return;
-    const int blk = blockIdx.x;
-    if (blk > total_blocks) return;  // blk == total_blocks is the all-zero block
-    const int c0 = blockIdx.y * 64;
-    int g = 0, i0 = 0, valid = 0;
-    if (blk < total_blocks) {
-        const int col = blk << 6;
-        int lo = 0, hi = G - 1;  // last g with pstart[g] <= col: the group that owns the block
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (pstart[mid] <= col) lo = mid; else hi = mid - 1;
-        }
-        g = lo;
-        i0 = col - pstart[g];
-        valid = min(64, (row_off[g + 1] - row_off[g]) - i0);
-    }
-    // load 64 rows x 64 columns (zeros outside), transposed through shared memory
-    const __nv_bfloat16* src_tile =
-        src + static_cast<size_t>(row_off[g] + i0) * ld + static_cast<size_t>(g) * col_group_stride + c0;
-    __nv_bfloat16* dst_tile = out + static_cast<size_t>(c0) * mpad + (static_cast<size_t>(blk) << 6);
-    transpose_tile_64(src_tile, ld, valid, min(64, C - c0), dst_tile, mpad, min(64, C - c0), 64, tile);
-}
-
-// Batched plain transpose: dst[b, c, r] = src[b, r, c]  (src [B, R, C], dst [B, C, R]).
-__global__ void __launch_bounds__(256)
-transpose_batched_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int R, int C) {
-    __shared__ __nv_bfloat16 tile[64][66];
-    const size_t base = static_cast<size_t>(blockIdx.z) * R * C;
-    const int r0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
-    transpose_tile_64(src + base + static_cast<size_t>(r0) * C + c0, C, min(64, R - r0), min(64, C - c0),
-                      dst + base + static_cast<size_t>(c0) * R + r0, R, min(64, C - c0), min(64, R - r0), tile);
+    __syncwarp();
 }
 
 struct DwSmemTail {
@@ -178,9 +72,8 @@ struct DwSmemTail {
     uint32_t tmem_base;
     int abort_flag;
     int invalid;
-    int total_blocks;
-    int koff[kMaxGroups + 1];
-    int kcnt[kMaxGroups + 1];
+    int kcnt[kMaxGroups + 1];     // 64-row blocks the group contracts
+    int row_off[kMaxGroups + 1];  // first row of the group in dY / X
 };
 
 template <int CTAS>
@@ -188,10 +81,57 @@ constexpr size_t dw_smem_bytes() {
     return 1024 + StageCfg<CTAS, 0>::kRingBytes + sizeof(DwSmemTail);
 }
 
-// tm_a: dYT [N rows, Mpad cols] (2-D map, box 128 x 64); tm_b: XT viewed as [1, K rows, Mpad cols].
+// Rows of group g's last block that are real: 0 = the block is whole (no side-buffer copy), 1..63 = that many
+// rows and zeros after them, 64 = empty group (the side buffer holds 64 zero rows to contract).
+__device__ __forceinline__ int tail_rows_of(int m) { return m <= 0 ? 64 : (m & 63); }
+
+// Side buffer: block g of dy_tail [G*64, N] and x_tail [G*64, K] is the zero-padded copy of
+// the group's partial last block.  grid = (G, ceil((N + K) / 8 / 256) rounded into y), 256 threads; every thread
+// moves 16 bytes (8 bf16) of one column chunk for all 64 rows.
+__global__ void __launch_bounds__(256)
+tail_pack_kernel(const __nv_bfloat16* __restrict__ dy, long long dy_ld, long long dy_col_group_stride,
+                 const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ m_sizes, int G, int M, int N, int K,
+                 __nv_bfloat16* __restrict__ dy_tail, __nv_bfloat16* __restrict__ x_tail) {
+    const int g = blockIdx.x;
+    __shared__ int s_row_end;
+    if (threadIdx.x < 32) {  // rows up to and including group g
+        int sum = 0;
+        for (int i = threadIdx.x; i <= g; i += 32) sum += max(m_sizes[i], 0);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+        if (threadIdx.x == 0) s_row_end = sum;
+    }
+    __syncthreads();
+    const int row_end = s_row_end, m = max(m_sizes[g], 0);
+    if (row_end > M) return;  // invalid sizes: the GEMM kernel reports them and writes nothing
+    const int valid = tail_rows_of(m);
+    if (valid == 0) return;  // whole last block: read in place
+    const int real = valid == 64 ? 0 : valid;
+    const long long first = static_cast<long long>(row_end) - real;  // first row of the partial block
+    const int chunk = blockIdx.y * 256 + threadIdx.x;                // 8-element column chunk over [dY | X]
+    const int n_chunks = N / 8, k_chunks = K / 8;
+    if (chunk >= n_chunks + k_chunks) return;
+    const bool is_dy = chunk < n_chunks;
+    const int c = (is_dy ? chunk : chunk - n_chunks) * 8;
+    const __nv_bfloat16* src = is_dy ? dy + first * dy_ld + g * dy_col_group_stride + c : x + first * K + c;
+    const long long src_ld = is_dy ? dy_ld : K;
+    __nv_bfloat16* dst = is_dy ? dy_tail + static_cast<long long>(g) * 64 * N + c
+                               : x_tail + static_cast<long long>(g) * 64 * K + c;
+    const int dst_ld = is_dy ? N : K;
+    for (int r = 0; r < 64; ++r) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < real) v = *reinterpret_cast<const uint4*>(src + r * src_ld);
+        *reinterpret_cast<uint4*>(dst + static_cast<long long>(r) * dst_ld) = v;
+    }
+}
+
+// tm_a = dY [M rows, ld cols], tm_b = X [M rows, K cols], tm_a_tail = dy_tail [G*64, N], tm_b_tail = x_tail
+// [G*64, K], all 2-D maps with boxes of 64 rows x 64 columns.
 template <int CTAS>
 __global__ void __launch_bounds__(kDwThreads, 1)
-gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const DWParams p) {
+gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+             const __grid_constant__ CUtensorMap tm_a_tail, const __grid_constant__ CUtensorMap tm_b_tail,
+             const DWParams p) {
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL)
     using Cfg = StageCfg<CTAS, 0>;
     constexpr int kTileRows = kRowsPerCta * CTAS;
@@ -215,7 +155,7 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     }
     __syncthreads();
     if (warp == 0) {
-        build_padded_layout(p.m_sizes, p.G, p.M, lane, st->koff, st->kcnt, &st->total_blocks, &st->invalid);
+        build_row_layout(p.m_sizes, p.G, p.M, lane, st->row_off, st->kcnt, &st->invalid);
         if (lane == 0) {
             if (st->invalid) report(p.status, kStatusBadGroupSizes);
             for (int s = 0; s < Cfg::kStages; ++s) {
@@ -255,7 +195,10 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                 const int n_idx = local % p.tiles_n, k_idx = local / p.tiles_n;
                 const int row0 = n_idx * kTileRows + static_cast<int>(cta_rank) * kRowsPerCta;
                 const int kcol0 = k_idx * kTileN;
-                const int koff = st->koff[g], nkb = st->kcnt[g];
+                const int nkb = st->kcnt[g];
+                // the group's rows, and whether its last block comes from the side buffer
+                const int grow0 = st->row_off[g];
+                const bool has_tail = tail_rows_of(st->row_off[g + 1] - grow0) != 0;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!__all_sync(0xffffffffu, mbar_wait(&st->empty[stage], phase ^ 1u, abort_flag))) {
                         report(p.status, kStatusTimeoutProducer);
@@ -264,21 +207,28 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                     }
                     const uint32_t a_dst = ring_addr + stage * Cfg::kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
-                    const int c0 = koff + kb * 64;
-                    if constexpr (CTAS == 1) {
-                        const uint32_t bar = smem_u32(&st->full[stage]);
-                        if (leader) {
-                            mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
-                            tma_load_2d(&tm_a, bar, a_dst, c0, row0);
-                            tma_load_3d(&tm_b, bar, b_dst, c0, kcol0, 0);
-                            tma_load_3d(&tm_b, bar, b_dst + kSubBoxBytes, c0, kcol0 + 128, 0);
-                        }
-                    } else {
-                        const uint32_t bar = mapa_shared(smem_u32(&st->full[stage]), 0);
-                        if (leader) {
-                            if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
-                            tma_load_2d_pair(&tm_a, bar, a_dst, c0, row0);
-                            tma_load_3d_pair(&tm_b, bar, b_dst, c0, kcol0 + static_cast<int>(cta_rank) * 128, 0);
+                    // boxes of 64 rows x 64 columns, 8192 bytes each: this CTA's 128 columns of dY (its rows
+                    // of dW) and its share of the tile's 256 columns of X
+                    const bool tail = has_tail && kb == nkb - 1;
+                    const CUtensorMap* ma = tail ? &tm_a_tail : &tm_a;
+                    const CUtensorMap* mb = tail ? &tm_b_tail : &tm_b;
+                    const int r = tail ? g * 64 : grow0 + kb * 64;
+                    const int ac = row0 + (tail ? 0 : static_cast<int>(g * p.dy_col_group_stride));
+                    const int bc = kcol0 + (CTAS == 2 ? static_cast<int>(cta_rank) * 128 : 0);
+                    const uint32_t bar =
+                        CTAS == 1 ? smem_u32(&st->full[stage]) : mapa_shared(smem_u32(&st->full[stage]), 0);
+                    if (leader) {
+                        if (cta_rank == 0) mbar_arrive_expect_tx(&st->full[stage], kTxBytes);
+                        if constexpr (CTAS == 1) {
+                            tma_load_2d(ma, bar, a_dst, ac, r);
+                            tma_load_2d(ma, bar, a_dst + 8192, ac + 64, r);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) tma_load_2d(mb, bar, b_dst + j * 8192, bc + j * 64, r);
+                        } else {
+                            tma_load_2d_pair(ma, bar, a_dst, ac, r);
+                            tma_load_2d_pair(ma, bar, a_dst + 8192, ac + 64, r);
+                            tma_load_2d_pair(mb, bar, b_dst, bc, r);
+                            tma_load_2d_pair(mb, bar, b_dst + 8192, bc + 64, r);
                         }
                     }
                     __syncwarp();
@@ -312,12 +262,14 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                     }
                     tc_fence_after();
                     const uint32_t a_addr = ring_addr + stage * Cfg::kStageBytes;
-                    const uint64_t a_desc = make_sw128_kmajor_desc(a_addr);
-                    const uint64_t b_desc = make_sw128_kmajor_desc(a_addr + kABytes);
+                    const uint64_t a_desc = make_sw128_mnmajor_desc(a_addr);
+                    const uint64_t b_desc = make_sw128_mnmajor_desc(a_addr + kABytes);
+                    // per MMA: 16 rows of 128 bytes of each tile, +128 in the descriptor's 16-byte units
+                    constexpr uint32_t kStep = 128u;
                     if (leader) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            umma<CTAS, false>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc,
+                            umma<CTAS, false>(d_tmem, a_desc + kStep * k, b_desc + kStep * k, p.idesc,
                                               (kb > 0 || k > 0) ? 1u : 0u);
                         umma_commit<CTAS>(&st->empty[stage]);
                     }
@@ -395,7 +347,8 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 }
 
 template <int CTAS>
-static int launch_dw(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const DWParams& p, int sms, cudaStream_t stream) {
+static int launch_dw(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_a_tail,
+                     const CUtensorMap& tm_b_tail, const DWParams& p, int sms, cudaStream_t stream) {
     auto kernel = gg_dw_kernel<CTAS>;
     constexpr size_t smem = dw_smem_bytes<CTAS>();
     static thread_local int configured_dev = -1;
@@ -418,49 +371,58 @@ static int launch_dw(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const DWP
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_a_tail, tm_b_tail, p);
     if (e == cudaSuccess) note_launch();
     return static_cast<int>(e);
 }
 
-long long dw_padded_cols(int M, int G) { return ((static_cast<long long>(M) + 63) / 64 + G + 1) * 64; }
-
-int transpose_pad_launch(const void* src, long long ld, long long col_group_stride, int C, const int32_t* m_sizes,
-                         int G, int M, void* out, long long mpad, cudaStream_t stream) {
-    if (src == nullptr || out == nullptr || m_sizes == nullptr || C <= 0 || G <= 0 || G > kMaxGroups || M < 0 ||
-        mpad < dw_padded_cols(M, G))
-        return kErrBadArgument;
-    const dim3 grid(static_cast<unsigned>(mpad / 64), static_cast<unsigned>((C + 63) / 64), 1);
-    transpose_pad_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), ld, col_group_stride, C,
-                                                   m_sizes, G, M, static_cast<__nv_bfloat16*>(out), mpad);
-    note_launch();
-    return static_cast<int>(cudaGetLastError());
+// A [rows, ld] bf16 matrix read as an MN-major operand: boxes of 64 rows x 64 columns, 128-byte swizzle.
+static int encode_mn_map_2d(CUtensorMap* m, const void* base, long long rows, long long ld) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return kErrNoDriverEntry;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    cuuint32_t box[2] = {64, 64};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
 }
 
-int transpose_batched_launch(const void* src, void* dst, int B, int R, int C, cudaStream_t stream) {
-    if (src == nullptr || dst == nullptr || B <= 0 || R <= 0 || C <= 0 || B > 65535) return kErrBadArgument;
-    const dim3 grid(static_cast<unsigned>((R + 63) / 64), static_cast<unsigned>((C + 63) / 64),
-                    static_cast<unsigned>(B));
-    transpose_batched_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src),
-                                                       static_cast<__nv_bfloat16*>(dst), R, C);
-    note_launch();
-    return static_cast<int>(cudaGetLastError());
+size_t dw_workspace_bytes(int N, int K, int G) {
+    return 2ull * 64ull * static_cast<size_t>(G) * (static_cast<size_t>(N) + K) + 256;
 }
 
-// dyt [N, mpad], xt [K, mpad] (outputs of transpose_pad_launch with the same m_sizes), dw [G, N, K].
-int grouped_gemm_dw_launch(const void* dyt, const void* xt, const int32_t* m_sizes, void* dw, int M, int N, int K,
-                           int G, long long mpad, int cta_group, int32_t* status, cudaStream_t stream) {
-    if (dyt == nullptr || xt == nullptr || m_sizes == nullptr || dw == nullptr || M < 0 || N <= 0 || K <= 0 ||
-        G <= 0 || mpad < dw_padded_cols(M, G) || (mpad % 8) != 0)
+// dy [M, dy_ld] (group g's block starts at column g * dy_col_group_stride), x [M, K], dw [G, N, K], all bf16 and
+// read / written in place; tail_ws: dw_workspace_bytes(N, K, G) bytes, 16-byte aligned.
+int grouped_gemm_dw_launch(const void* dy, long long dy_ld, long long dy_col_group_stride, const void* x,
+                                  const int32_t* m_sizes, void* dw, int M, int N, int K, int G, void* tail_ws,
+                                  int cta_group, int32_t* status, cudaStream_t stream) {
+    if (dy == nullptr || x == nullptr || m_sizes == nullptr || dw == nullptr || tail_ws == nullptr || M <= 0 ||
+        N <= 0 || K <= 0 || G <= 0 || dy_ld < N || dy_col_group_stride < 0)
         return kErrBadArgument;
     if (G > kMaxGroups) return kErrTooManyGroups;
-    if ((reinterpret_cast<uintptr_t>(dyt) & 15u) || (reinterpret_cast<uintptr_t>(xt) & 15u)) return kErrAlignment;
+    if (N % 8 != 0 || K % 8 != 0 || dy_ld % 8 != 0 || dy_col_group_stride % 8 != 0 ||
+        (reinterpret_cast<uintptr_t>(dy) & 15u) || (reinterpret_cast<uintptr_t>(x) & 15u) ||
+        (reinterpret_cast<uintptr_t>(tail_ws) & 15u))
+        return kErrAlignment;
     DeviceInfo di;
     if (int e = get_device_info(&di)) return e;
     if (di.cc_major != 10) return kErrWrongDevice;
-    CUtensorMap tm_a, tm_b;
-    if (int e = encode_x_map(&tm_a, dyt, N, static_cast<int>(mpad), 2)) return e;
-    if (int e = encode_w_map(&tm_b, xt, 1, K, static_cast<int>(mpad), 2)) return e;
+    __nv_bfloat16* dy_tail = static_cast<__nv_bfloat16*>(tail_ws);
+    __nv_bfloat16* x_tail = dy_tail + 64ull * G * N;  // 128 * G * N bytes in: still 16-byte aligned
+    CUtensorMap tm_a, tm_b, tm_a_tail, tm_b_tail;
+    if (int e = encode_mn_map_2d(&tm_a, dy, M, dy_ld)) return e;
+    if (int e = encode_mn_map_2d(&tm_b, x, M, K)) return e;
+    if (int e = encode_mn_map_2d(&tm_a_tail, dy_tail, 64ll * G, N)) return e;
+    if (int e = encode_mn_map_2d(&tm_b_tail, x_tail, 64ll * G, K)) return e;
+    const dim3 grid(static_cast<unsigned>(G), static_cast<unsigned>(((N + K) / 8 + 255) / 256), 1);
+    tail_pack_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy), dy_ld, dy_col_group_stride,
+                                               static_cast<const __nv_bfloat16*>(x), m_sizes, G, M, N, K, dy_tail,
+                                               x_tail);
+    if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return static_cast<int>(e);
+    note_launch();
     const int ctas = cta_group == 1 ? 1 : cta_group == 2 ? 2 : (N >= 256 ? 2 : 1);
     DWParams p;
     p.m_sizes = m_sizes;
@@ -472,8 +434,10 @@ int grouped_gemm_dw_launch(const void* dyt, const void* xt, const int32_t* m_siz
     p.G = G;
     p.tiles_n = (N + 128 * ctas - 1) / (128 * ctas);
     p.tiles_k = (K + kTileN - 1) / kTileN;
-    p.idesc = make_idesc(false, 128 * ctas, kTileN);
-    return ctas == 1 ? launch_dw<1>(tm_a, tm_b, p, di.sms, stream) : launch_dw<2>(tm_a, tm_b, p, di.sms, stream);
+    p.idesc = make_idesc(false, 128 * ctas, kTileN, false, true, true);
+    p.dy_col_group_stride = dy_col_group_stride;
+    return ctas == 1 ? launch_dw<1>(tm_a, tm_b, tm_a_tail, tm_b_tail, p, di.sms, stream)
+                     : launch_dw<2>(tm_a, tm_b, tm_a_tail, tm_b_tail, p, di.sms, stream);
 }
 
 }  // namespace b200moe

@@ -228,14 +228,31 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
     return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major 16-bit operand tile (the operand's own dimension M or N is
+// the contiguous one in memory, the contraction index walks the rows).  TMA wrote it with the 128-byte swizzle
+// as boxes of 64 contraction rows x 64 elements (128 bytes): inside a box the rows are 128 bytes apart, so
+// 8-row groups are 1024 bytes apart (the stride offset), and the next 64 elements of the operand's own
+// dimension sit one whole box further on (the leading offset, 8192 bytes).  One K = 16 MMA reads 16 rows:
+// the next one starts 2048 bytes further on.
+__device__ __forceinline__ uint64_t make_sw128_mnmajor_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(8192 >> 4) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
 // Instruction descriptor for kind::f16 (bf16 x bf16) or kind::f8f6f4 (e4m3 x e4m3),
-// fp32 accumulate, both operands K-major.
+// fp32 accumulate, operands K-major unless a_mn_major / b_mn_major.
 // Bits: [4,6) D format (1 = f32), [7,10) A format, [10,13) B format,
-// [15] A major, [16] B major (0 = K), [17,23) N>>3, [24,29) M>>4.
-__host__ __device__ constexpr uint32_t make_idesc(bool is_fp8, int mma_m, int mma_n, bool is_f16 = false) {
+// [15] A major, [16] B major (0 = K, 1 = MN), [17,23) N>>3, [24,29) M>>4.
+__host__ __device__ constexpr uint32_t make_idesc(bool is_fp8, int mma_m, int mma_n, bool is_f16 = false,
+                                                  bool b_mn_major = false, bool a_mn_major = false) {
     const uint32_t fmt = is_fp8 ? 0u /* E4M3 */ : (is_f16 ? 0u /* F16 */ : 1u /* BF16 */);
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(mma_n >> 3) << 17) |
-           (static_cast<uint32_t>(mma_m >> 4) << 24);
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn_major ? (1u << 15) : 0u) | (b_mn_major ? (1u << 16) : 0u) |
+           (static_cast<uint32_t>(mma_n >> 3) << 17) | (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
 
 // One lane of a converged warp.  The MMA issuer walks its loop with the whole warp so that

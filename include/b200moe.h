@@ -201,8 +201,10 @@ int b200moe_sm100_gemm_f16(const void* A, const void* B, const void* C, void* D,
  * (grad_y_ld = N, stride 0), bf16.  Rows of grad_x past sum(m_sizes) are not written.
  * Replaces grouped_gemm_backward(grad_output, x, w, m_sizes)
  *   kernels/MoE/group_GEMM/triton/tgroup_gemm_backwards.py:382 (per-group definition:
- *   testing/pytorch_reference_backwards.py:165-197).  `workspace` holds transposed copies
- * (b200moe_backward_workspace_bytes). */
+ *   testing/pytorch_reference_backwards.py:165-197).  grad_y, x and w are read where they lie (N, K,
+ * grad_y_ld and grad_y_col_group_stride must be multiples of 8, else B200MOE_EALIGN); `workspace`
+ * (b200moe_backward_workspace_bytes: 128 * G * (N + K) bytes and some slack) holds the zero-padded copies of
+ * the groups' last partial 64-row blocks that grad_w contracts over. */
 int b200moe_backward_workspace_bytes(int M, int N, int K, int G, size_t* bytes);
 int b200moe_grouped_gemm_backward(const void* grad_y, const void* x, const void* w, const int32_t* m_sizes,
                                   void* grad_x, void* grad_w, int M, int N, int K, int G, int64_t grad_y_ld,
