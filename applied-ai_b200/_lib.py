@@ -64,6 +64,7 @@ SIGNATURES = {
     "b200moe_grouped_gemm_backward": [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_i64,
                                       _c_i64, _c_vp, _c_sz, _c_int, _c_vp, _c_vp],
     "b200moe_selftest_wait_timeout": [ctypes.c_uint64, _c_vp, _c_vp],
+    "b200moe_selftest_tmem_read": [_c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp],
     "b200moe_route_workspace_bytes": [_c_int, _c_int, ctypes.POINTER(_c_sz)],
     "b200moe_route": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp],
     "b200moe_route_noalloc": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp],

@@ -98,6 +98,8 @@ int grouped_gemm_dw_launch(const void* dy, long long dy_ld, long long dy_col_gro
                            const int32_t* m_sizes, void* dw, int M, int N, int K, int G, void* tail_ws,
                            int cta_group, int32_t* status, cudaStream_t stream);
 int selftest_wait_launch(uint64_t limit_ns, int32_t* status, cudaStream_t stream);
+int selftest_tmem_read_launch(int warps, int in_flight, int iters, int ctas, long long* cycles_out,
+                              cudaStream_t stream);
 // FP8 with 1x128 activation scales [M, K/128] and 128x128 weight scales [G, ceil(N/128), K/128].
 int grouped_gemm_fp8_block_launch(const GGLaunch& a);
 

@@ -278,6 +278,11 @@ int b200moe_selftest_wait_timeout(uint64_t limit_ns, int32_t* status, b200moe_st
     return selftest_wait_launch(limit_ns, status, static_cast<cudaStream_t>(stream));
 }
 
+int b200moe_selftest_tmem_read(int warps, int in_flight, int iters, int ctas, long long* cycles,
+                               b200moe_stream_t stream) {
+    return selftest_tmem_read_launch(warps, in_flight, iters, ctas, cycles, static_cast<cudaStream_t>(stream));
+}
+
 int b200moe_route_workspace_bytes(int R, int E, size_t* bytes) {
     if (bytes == nullptr) return kErrBadArgument;
     int chunk_len = 0, num_chunks = 0;

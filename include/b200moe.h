@@ -218,6 +218,14 @@ int b200moe_grouped_gemm_backward(const void* grad_y, const void* x, const void*
  * 16..19, limit 0.4 s).  No counterpart in the reference, which has no bounded waits. */
 int b200moe_selftest_wait_timeout(uint64_t limit_ns, int32_t* status, b200moe_stream_t stream);
 
+/* Diagnostic without a counterpart in the reference: the raw rate of tcgen05.ld.  `ctas` CTAs of `warps` (4 or
+ * 8) warps each read one 128-lane x 256-column fp32 accumulator (128 KiB of tensor memory) `iters` times with
+ * 32x32b.x32 loads, `in_flight` (1, 2 or 4) loads issued before each wait; cycles[cta] (device memory, `ctas`
+ * entries) receives the SM clock ticks of the loop.  128 KiB * iters / cycles is the bytes per clock an
+ * epilogue, or the per-K-block promotion of the block-wise FP8 kernel, can at best drain. */
+int b200moe_selftest_tmem_read(int warps, int in_flight, int iters, int ctas, long long* cycles,
+                               b200moe_stream_t stream);
+
 /* Routing: stable counting sort of ids[R] (R = tokens*top_k, flat index t*top_k + j)
  * by expert.  m_sizes[E], offsets[E+1], perm[R] (sorted position -> flat index),
  * inv_perm[R] (flat index -> sorted position, -1 for an id outside [0,E)).

@@ -65,3 +65,15 @@ def test_stream_barrier_gives_up_on_a_peer_that_never_signals():
     # bad arguments are refused on the host
     assert lib.b200moe_ep_barrier(table.data_ptr(), P, 2, 0, 1, 50_000_000, status.data_ptr(), stream) == -1
     assert lib.b200moe_ep_barrier(table.data_ptr(), P, 0, 0, 1, 0, status.data_ptr(), stream) == -1
+
+
+def test_tmem_read_probe_reports_a_plausible_rate():
+    """The diagnostic runs, leaves the context usable and reports a rate between 16 B/clk (one lane quadrant
+    crawling) and 4 KiB/clk (more than the MMA itself moves) per SM."""
+    from applied_ai_b200.selftest import tmem_read_rate
+    for warps, in_flight in ((4, 1), (8, 2)):
+        r = tmem_read_rate(warps, in_flight, iters=50, ctas=4)
+        assert 16.0 < r < 4096.0
+    with pytest.raises(Exception):
+        tmem_read_rate(warps=3)
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
