@@ -72,3 +72,35 @@ def test_random_groups_and_errors():
     with pytest.raises(RuntimeError):
         grouped_gemm_backward(dy.to(DEV)[:, :100].contiguous(), x.to(DEV), w.to(DEV),
                               torch.full((G,), 128, dtype=torch.int32, device=DEV))
+
+
+def test_full_size_deepseek_gate_up_shape_sampled():
+    """The bench's backward shape (G=8, K=7168, N=4096, M=16384, ragged groups with partial 64-row blocks) against
+    the oracle on what it can do in seconds: grad_x on sampled rows of every group (rows are independent, so the
+    oracle runs on the sampled rows with the per-group counts), grad_w on sampled rows n of w in every group
+    (grad_w[g][n] depends on column n of grad_output only)."""
+    g = torch.Generator().manual_seed(63)
+    G, M, N, K = 8, 16384, 4096, 7168
+    m = random_m_sizes(G, M - 300, g)          # ragged, sum < M
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(G, N, K, generator=g) * K ** -0.5).to(torch.bfloat16)
+    dy = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    gx, gw = grouped_gemm_backward(dy.to(DEV), x.to(DEV), w.to(DEV), m.to(DEV))
+    gx, gw = gx.cpu().float(), gw.cpu().float()
+    # grad_x: first, last and two random rows of every non-empty group
+    starts = torch.cumsum(m, 0) - m
+    rows, counts = [], []
+    for e in range(G):
+        n_e = int(m[e])
+        pick = sorted({0, n_e - 1, *torch.randint(0, max(n_e, 1), (2,), generator=g).tolist()}) if n_e else []
+        rows += [int(starts[e]) + r for r in pick]
+        counts.append(len(pick))
+    rows = torch.tensor(rows)
+    rx, _ = O.grouped_gemm_backward_ref(dy[rows], x[rows], w, torch.tensor(counts, dtype=torch.int32))
+    assert O.rel_err(gx[rows], rx) <= BF16_REL_TOL
+    assert bool((gx[int(m.sum()):] == 0).all())
+    # grad_w: 6 sampled rows n, all groups, all K
+    ns = torch.randint(0, N, (6,), generator=g)
+    _, rw = O.grouped_gemm_backward_ref(dy[:, ns].contiguous(), x, w[:, ns].contiguous(), m)
+    assert O.rel_err(gw[:, ns], rw) <= BF16_REL_TOL
+    assert torch.allclose(gw[:, ns], rw, rtol=1e-2, atol=1e-2 * max(1.0, float(rw.abs().max())))
