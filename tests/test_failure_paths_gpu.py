@@ -77,3 +77,55 @@ def test_tmem_read_probe_reports_a_plausible_rate():
     with pytest.raises(Exception):
         tmem_read_rate(warps=3)
     assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+def test_two_host_threads_on_their_own_streams_get_the_serial_results():
+    """The entry points keep no state that two callers could share by accident: two Python threads, each on its
+    own stream and with its own shapes (bf16 forward, backward, block-wise FP8 with a bad-size call in between),
+    produce bit for bit what the same calls produce one after another, and the bad call of one thread does not
+    show up in the other thread's status word."""
+    import threading
+    from applied_ai_b200.tgroup_gemm_backwards import grouped_gemm_backward
+
+    def inputs(seed, G, M, N, K):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(G, N, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+        dy = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+        m = torch.full((G,), M // G - 3, dtype=torch.int32).cuda()
+        return x, w, dy, m
+
+    def work(args, bad):
+        x, w, dy, m = args
+        out = []
+        for it in range(6):
+            out.append(B.grouped_gemm(x, w, m))
+            out.extend(grouped_gemm_backward(dy, x, w, m))
+            if bad and it == 2:
+                with pytest.raises(ValueError):
+                    B.grouped_gemm(x, w, torch.full_like(m, x.shape[0]))  # sum(m_sizes) > M
+        torch.cuda.current_stream().synchronize()
+        return out
+
+    cases = [(inputs(71, 4, 1024, 512, 256), True), (inputs(72, 6, 1536, 384, 640), False)]
+    serial = [work(a, bad) for a, bad in cases]
+    results, errors = [None, None], []
+
+    def runner(i):
+        try:
+            with torch.cuda.stream(torch.cuda.Stream()):
+                results[i] = work(*cases[i])
+        except Exception as e:  # noqa: BLE001 - reported below
+            errors.append(e)
+
+    threads = [threading.Thread(target=runner, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors, errors
+    for got, want in zip(results, serial):
+        assert got is not None and len(got) == len(want)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+    assert B.pending_status() is None
