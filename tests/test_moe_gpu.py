@@ -157,3 +157,34 @@ def test_full_size_mixtral_layer():
     got_rows = out[pick.to(DEV)].cpu().float()
     assert O.rel_err(got_rows, ref) <= BF16_REL_TOL
     assert torch.allclose(got_rows, ref, atol=1e-2 * float(ref.abs().max()), rtol=1.6e-2)
+
+
+def test_fused_moe_replays_from_a_cuda_graph():
+    """With check=False the layer is a fixed sequence of launches on the current stream (no host read, no
+    allocation outside torch's caching allocator), so it can be captured once and replayed on new inputs and
+    new routing written into the same tensors."""
+    T, H, I, E, k = 256, 512, 768, 8, 2
+    hidden, w1, w2, tw, ids = (t.to(DEV) for t in C.c3_mixtral_layer(T=T, H=H, I=I, E=E, k=k, seed=1002))
+    hidden2, _, _, tw2, ids2 = (t.to(DEV) for t in C.c3_mixtral_layer(T=T, H=H, I=I, E=E, k=k, seed=2002))
+    want1 = B.fused_moe(hidden, w1, w2, tw, ids)
+    want2 = B.fused_moe(hidden2, w1, w2, tw2, ids2)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):  # first calls on this stream create its status word and workspace
+            B.fused_moe(hidden, w1, w2, tw, ids, check=False)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        out = B.fused_moe(hidden, w1, w2, tw, ids, check=False)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want1)
+    hidden.copy_(hidden2)
+    tw.copy_(tw2)
+    ids.copy_(ids2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want2)
+    assert B.pending_status() is None
