@@ -53,6 +53,9 @@ struct GGParams {
     int n_out;    // output columns per group (N, or N/2 with SwiGLU)
     int n_tiles;  // column tiles per group
     int tile_mode;  // which row blocks this launch covers (kTilesAll / kTilesMain / kTilesTails)
+    int overlap_role;  // 0 none; 1: a second launch of the same GEMM follows and may start on the SMs this one gives
+                       // back (launch_dependents at start); 2: that second launch (griddep_wait before it exits, so
+                       // that it never completes before the first one)
 };
 
 struct GGLaunch {

@@ -387,6 +387,7 @@ int grouped_gemm_launch(const GGLaunch& a) {
     const bool split_tails = false;
     auto launch = [&](int nctas, int mode) -> int {
         p.tile_mode = mode;
+        p.overlap_role = 0;
         p.idesc = make_idesc(fp8, 128 * nctas, kTileN, a.is_f16 != 0, a.w_mn_major != 0);
         p.idesc_half = make_idesc(fp8, 128 * nctas, kTileN / 2, a.is_f16 != 0, a.w_mn_major != 0);
         if (a.w_mn_major)

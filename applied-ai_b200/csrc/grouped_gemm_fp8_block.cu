@@ -138,6 +138,9 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const uint32_t tmem_base = st->tmem_base;
     const int total_tiles = st->total_tiles;
     const int num_kb = p.K / 128;  // the launcher guarantees K % 128 == 0
+    // main launch of a main + tails pair: the tails kernel writes other rows and needs nothing from this one, so
+    // its CTAs may take each SM as soon as this kernel's CTA there is done
+    if (p.overlap_role == 1 && threadIdx.x == 0) griddep_launch_dependents();
 
     // Register budget: one light warpgroup + two promotion warpgroups (see B200MOE_BLK_*_REGS).
     if (warp < 4) {
@@ -556,6 +559,8 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         tc_fence_after();
         tmem_dealloc<CTAS>(tmem_base, kTmemCols);
     }
+    // tails launch: what follows in the stream waits for this kernel only, so it must not end before the main one
+    if (p.overlap_role == 2 && threadIdx.x == 0) griddep_wait();
 #else
     if (threadIdx.x == 0 && blockIdx.x == 0) report(p.status, kStatusWrongArch);
 #endif
@@ -564,6 +569,7 @@ gg_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 template <int CTAS, int EPI, bool BULK = false>
 static int launch_block_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const GGParams& p, int sms,
                                 cudaStream_t stream) {
+    const bool overlapped = p.overlap_role == 2;  // may start before the kernel in front of it has finished
     auto kernel = gg_fp8_block_kernel<CTAS, EPI, BULK>;
     constexpr size_t smem = gg_smem_bytes<CTAS, BULK ? BulkCfg<EPI, CTAS>::kLess : 0,
                                            BULK ? BulkCfg<EPI, CTAS>::kStagingBytes + (EPI == 3 ? 2304 : 0)
@@ -582,13 +588,15 @@ static int launch_block_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w
     cfg.blockDim = dim3(kBlkThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = overlapped ? 2 : 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, p);
     if (e == cudaSuccess) note_launch();
     return static_cast<int>(e);
@@ -670,6 +678,7 @@ int grouped_gemm_fp8_block_launch(const GGLaunch& a) {
     const bool split_tails = a.cta_group == 0 && ctas == 2;
     auto launch = [&](int nctas, int mode) -> int {
         p.tile_mode = mode;
+        p.overlap_role = mode == kTilesMain ? 1 : (mode == kTilesTails ? 2 : 0);
         p.idesc = make_idesc(true, 128 * nctas, kTileN);
         p.idesc_half = p.idesc;
         if (a.epilogue == 3)  // (its argument checks above already demand aligned, whole 128-column runs)
