@@ -76,6 +76,7 @@ struct GGLaunch {
     float alpha, beta;
     int is_f16;      // 2-byte operands are IEEE half instead of bf16
     int w_mn_major;  // w is [G, K, N] (N contiguous) instead of [G, N, K]; 16-bit operands, plain epilogue only
+    int overlap_role;  // GGParams::overlap_role for a caller that pairs this launch with an independent one
     int y_rows;
     long long ldy;
     long long y_col_group_stride;
@@ -97,9 +98,14 @@ int grouped_gemm_launch(const GGLaunch& a);
 // Weight gradient (grouped_gemm_dw.cu): dY [M, dy_ld] and x [M, K] are read in place; tail_ws holds the
 // zero-padded copies of the groups' partial last 64-row blocks (dw_workspace_bytes).
 size_t dw_workspace_bytes(int N, int K, int G);
+// Step 1 (tail_pack_kernel) fills tail_ws; step 2 is the GEMM.  overlapped: the kernel launched just before in
+// the stream is independent of this one and has executed launch_dependents, so this one may start on the SMs
+// that one gives back (it then waits for that kernel before it exits).
+int dw_tail_pack_launch(const void* dy, long long dy_ld, long long dy_col_group_stride, const void* x,
+                        const int32_t* m_sizes, int M, int N, int K, int G, void* tail_ws, cudaStream_t stream);
 int grouped_gemm_dw_launch(const void* dy, long long dy_ld, long long dy_col_group_stride, const void* x,
-                           const int32_t* m_sizes, void* dw, int M, int N, int K, int G, void* tail_ws,
-                           int cta_group, int32_t* status, cudaStream_t stream);
+                           const int32_t* m_sizes, void* dw, int M, int N, int K, int G, const void* tail_ws,
+                           int cta_group, bool overlapped, int32_t* status, cudaStream_t stream);
 int selftest_wait_launch(uint64_t limit_ns, int32_t* status, cudaStream_t stream);
 int selftest_tmem_read_launch(int warps, int in_flight, int iters, int ctas, long long* cycles_out,
                               cudaStream_t stream);

@@ -248,12 +248,20 @@ int b200moe_grouped_gemm_backward(const void* grad_y, const void* x, const void*
     if (workspace_bytes < need) return kErrTooLarge;
     if (M == 0) return 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The two gradients are independent of each other, so the grad_w kernel is launched to start on the SMs the
+    // grad_x kernel gives back while its last round of tiles drains (overlap_role); the small packing kernel that
+    // grad_w needs runs first so that nothing stands between the two.
+    const uintptr_t tail_ws = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~static_cast<uintptr_t>(255);
+    if (int e = dw_tail_pack_launch(grad_y, grad_y_ld, grad_y_col_group_stride, x, m_sizes, M, N, K, G,
+                                    reinterpret_cast<void*>(tail_ws), s))
+        return e;
     // grad_x[rows of g] = grad_y[rows of g, block g] @ w[g]: the forward kernel with w[g] [N, K] read as an
     // MN-major operand (the contraction walks its rows)
     GGLaunch a{};
     a.x = grad_y;
     a.w = w;
     a.w_mn_major = 1;
+    a.overlap_role = 1;
     a.m_sizes = m_sizes;
     a.y = grad_x;
     a.status = status;
@@ -269,9 +277,8 @@ int b200moe_grouped_gemm_backward(const void* grad_y, const void* x, const void*
     a.stream = s;
     if (int e = grouped_gemm_launch(a)) return e;
     // grad_w[g] = grad_y[rows of g, block g]^T @ x[rows of g]
-    const uintptr_t tail_ws = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~static_cast<uintptr_t>(255);
     return grouped_gemm_dw_launch(grad_y, grad_y_ld, grad_y_col_group_stride, x, m_sizes, grad_w, M, N, K, G,
-                                  reinterpret_cast<void*>(tail_ws), cta_group, status, s);
+                                  reinterpret_cast<const void*>(tail_ws), cta_group, /*overlapped=*/true, status, s);
 }
 
 int b200moe_selftest_wait_timeout(uint64_t limit_ns, int32_t* status, b200moe_stream_t stream) {

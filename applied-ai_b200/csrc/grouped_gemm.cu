@@ -81,6 +81,8 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
     const uint32_t tmem_base = st->tmem_base;
     const int total_tiles = st->total_tiles;
     const int num_kb = (p.K + kElemsPerStage - 1) / kElemsPerStage;
+    // an independent kernel follows in the stream: its CTAs may take each SM as soon as this kernel's CTA there is done
+    if (p.overlap_role == 1 && threadIdx.x == 0) griddep_launch_dependents();
     const WorkSplit ws = make_work_split(total_tiles, num_clusters, CTAS == 2);
 
     if (warp == 0) {
@@ -269,6 +271,8 @@ gg_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUte
         tc_fence_after();
         tmem_dealloc<CTAS>(tmem_base, kTmemCols);
     }
+    // started early, beside an independent kernel: do not end before that one (what follows waits for this one only)
+    if (p.overlap_role == 2 && threadIdx.x == 0) griddep_wait();
 #else
     if (threadIdx.x == 0 && blockIdx.x == 0) report(p.status, kStatusWrongArch);
 #endif
@@ -295,13 +299,15 @@ static int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, cons
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = p.overlap_role == 2 ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, p);
     if (e == cudaSuccess) note_launch();
     return static_cast<int>(e);
@@ -387,7 +393,7 @@ int grouped_gemm_launch(const GGLaunch& a) {
     const bool split_tails = false;
     auto launch = [&](int nctas, int mode) -> int {
         p.tile_mode = mode;
-        p.overlap_role = 0;
+        p.overlap_role = a.overlap_role;
         p.idesc = make_idesc(fp8, 128 * nctas, kTileN, a.is_f16 != 0, a.w_mn_major != 0);
         p.idesc_half = make_idesc(fp8, 128 * nctas, kTileN / 2, a.is_f16 != 0, a.w_mn_major != 0);
         if (a.w_mn_major)

@@ -27,6 +27,7 @@ struct DWParams {
     int M, N, K, G;     // M = rows of x / dY; N, K = weight dims
     int tiles_n, tiles_k;
     uint32_t idesc;
+    int overlapped;                 // launched beside the independent kernel in front of it: wait for that one before exiting
     long long dy_col_group_stride;  // first column of group g's block of dY = g * this
 };
 
@@ -341,6 +342,7 @@ gg_dw_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         tc_fence_after();
         tmem_dealloc<CTAS>(tmem_base, kTmemCols);
     }
+    if (p.overlapped && threadIdx.x == 0) griddep_wait();
 #else
     if (threadIdx.x == 0 && blockIdx.x == 0) report(p.status, kStatusWrongArch);
 #endif
@@ -364,13 +366,15 @@ static int launch_dw(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUt
     cfg.blockDim = dim3(kDwThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = p.overlapped ? 2 : 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_a_tail, tm_b_tail, p);
     if (e == cudaSuccess) note_launch();
     return static_cast<int>(e);
@@ -395,34 +399,50 @@ size_t dw_workspace_bytes(int N, int K, int G) {
 }
 
 // dy [M, dy_ld] (group g's block starts at column g * dy_col_group_stride), x [M, K], dw [G, N, K], all bf16 and
-// read / written in place; tail_ws: dw_workspace_bytes(N, K, G) bytes, 16-byte aligned.
-int grouped_gemm_dw_launch(const void* dy, long long dy_ld, long long dy_col_group_stride, const void* x,
-                                  const int32_t* m_sizes, void* dw, int M, int N, int K, int G, void* tail_ws,
-                                  int cta_group, int32_t* status, cudaStream_t stream) {
-    if (dy == nullptr || x == nullptr || m_sizes == nullptr || dw == nullptr || tail_ws == nullptr || M <= 0 ||
-        N <= 0 || K <= 0 || G <= 0 || dy_ld < N || dy_col_group_stride < 0)
+// read / written in place; tail_ws: dw_workspace_bytes(N, K, G) bytes, 16-byte aligned, filled by
+// dw_tail_pack_launch with the same arguments.
+static int check_dw_args(const void* dy, long long dy_ld, long long dy_col_group_stride, const void* x,
+                         const int32_t* m_sizes, int M, int N, int K, int G, const void* tail_ws) {
+    if (dy == nullptr || x == nullptr || m_sizes == nullptr || tail_ws == nullptr || M <= 0 || N <= 0 || K <= 0 ||
+        G <= 0 || dy_ld < N || dy_col_group_stride < 0)
         return kErrBadArgument;
     if (G > kMaxGroups) return kErrTooManyGroups;
     if (N % 8 != 0 || K % 8 != 0 || dy_ld % 8 != 0 || dy_col_group_stride % 8 != 0 ||
         (reinterpret_cast<uintptr_t>(dy) & 15u) || (reinterpret_cast<uintptr_t>(x) & 15u) ||
         (reinterpret_cast<uintptr_t>(tail_ws) & 15u))
         return kErrAlignment;
-    DeviceInfo di;
-    if (int e = get_device_info(&di)) return e;
-    if (di.cc_major != 10) return kErrWrongDevice;
+    return 0;
+}
+
+int dw_tail_pack_launch(const void* dy, long long dy_ld, long long dy_col_group_stride, const void* x,
+                        const int32_t* m_sizes, int M, int N, int K, int G, void* tail_ws, cudaStream_t stream) {
+    if (int e = check_dw_args(dy, dy_ld, dy_col_group_stride, x, m_sizes, M, N, K, G, tail_ws)) return e;
     __nv_bfloat16* dy_tail = static_cast<__nv_bfloat16*>(tail_ws);
     __nv_bfloat16* x_tail = dy_tail + 64ull * G * N;  // 128 * G * N bytes in: still 16-byte aligned
-    CUtensorMap tm_a, tm_b, tm_a_tail, tm_b_tail;
-    if (int e = encode_mn_map_2d(&tm_a, dy, M, dy_ld)) return e;
-    if (int e = encode_mn_map_2d(&tm_b, x, M, K)) return e;
-    if (int e = encode_mn_map_2d(&tm_a_tail, dy_tail, 64ll * G, N)) return e;
-    if (int e = encode_mn_map_2d(&tm_b_tail, x_tail, 64ll * G, K)) return e;
     const dim3 grid(static_cast<unsigned>(G), static_cast<unsigned>(((N + K) / 8 + 255) / 256), 1);
     tail_pack_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy), dy_ld, dy_col_group_stride,
                                                static_cast<const __nv_bfloat16*>(x), m_sizes, G, M, N, K, dy_tail,
                                                x_tail);
     if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return static_cast<int>(e);
     note_launch();
+    return 0;
+}
+
+int grouped_gemm_dw_launch(const void* dy, long long dy_ld, long long dy_col_group_stride, const void* x,
+                           const int32_t* m_sizes, void* dw, int M, int N, int K, int G, const void* tail_ws,
+                           int cta_group, bool overlapped, int32_t* status, cudaStream_t stream) {
+    if (dw == nullptr) return kErrBadArgument;
+    if (int e = check_dw_args(dy, dy_ld, dy_col_group_stride, x, m_sizes, M, N, K, G, tail_ws)) return e;
+    DeviceInfo di;
+    if (int e = get_device_info(&di)) return e;
+    if (di.cc_major != 10) return kErrWrongDevice;
+    const __nv_bfloat16* dy_tail = static_cast<const __nv_bfloat16*>(tail_ws);
+    const __nv_bfloat16* x_tail = dy_tail + 64ull * G * N;
+    CUtensorMap tm_a, tm_b, tm_a_tail, tm_b_tail;
+    if (int e = encode_mn_map_2d(&tm_a, dy, M, dy_ld)) return e;
+    if (int e = encode_mn_map_2d(&tm_b, x, M, K)) return e;
+    if (int e = encode_mn_map_2d(&tm_a_tail, dy_tail, 64ll * G, N)) return e;
+    if (int e = encode_mn_map_2d(&tm_b_tail, x_tail, 64ll * G, K)) return e;
     const int ctas = cta_group == 1 ? 1 : cta_group == 2 ? 2 : (N >= 256 ? 2 : 1);
     DWParams p;
     p.m_sizes = m_sizes;
@@ -435,6 +455,7 @@ int grouped_gemm_dw_launch(const void* dy, long long dy_ld, long long dy_col_gro
     p.tiles_n = (N + 128 * ctas - 1) / (128 * ctas);
     p.tiles_k = (K + kTileN - 1) / kTileN;
     p.idesc = make_idesc(false, 128 * ctas, kTileN, false, true, true);
+    p.overlapped = overlapped ? 1 : 0;
     p.dy_col_group_stride = dy_col_group_stride;
     return ctas == 1 ? launch_dw<1>(tm_a, tm_b, tm_a_tail, tm_b_tail, p, di.sms, stream)
                      : launch_dw<2>(tm_a, tm_b, tm_a_tail, tm_b_tail, p, di.sms, stream);
