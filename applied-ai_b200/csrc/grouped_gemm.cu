@@ -388,8 +388,10 @@ int grouped_gemm_launch(const GGLaunch& a) {
     // single-CTA launch) is NOT used here: this kernel is bound by the MMAs, a 128x256 single-CTA tile keeps
     // one SM busy about as long as the half-empty pair tile keeps two, and the second launch adds its own
     // partial wave.  Mixtral-shaped layer (8 groups of ~1024 rows, half of them with such a block):
-    // gate+up 1.458 ms split vs 1.430 ms pairs only, down 0.744 vs 0.720.  (The block-wise FP8 kernel, which is
-    // bound by latency instead, gains 5-10 % from it.)
+    // gate+up 1.458 ms split vs 1.430 ms pairs only, down 0.744 vs 0.720.  With the second launch started on the
+    // SMs the first gives back (overlap_role, as the block-wise kernel does) it still loses: DeepSeek gate+up shape
+    // 0.686 vs 0.668 ms, the Mixtral layer 2.29-2.30 vs 2.25-2.27 ms.  (The block-wise FP8 kernel, which is bound
+    // by latency instead, gains 5-10 % from the split.)
     const bool split_tails = false;
     auto launch = [&](int nctas, int mode) -> int {
         p.tile_mode = mode;
