@@ -98,8 +98,9 @@ def test_two_host_threads_on_their_own_streams_get_the_serial_results():
     def work(args, bad):
         x, w, dy, m = args
         out = []
+        rows = int(m.sum())
         for it in range(6):
-            out.append(B.grouped_gemm(x, w, m))
+            out.append(B.grouped_gemm(x, w, m)[:rows])  # (rows past sum(m_sizes) are not written: torch.empty)
             out.extend(grouped_gemm_backward(dy, x, w, m))
             if bad and it == 2:
                 with pytest.raises(ValueError):
