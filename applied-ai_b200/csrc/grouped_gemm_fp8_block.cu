@@ -26,6 +26,10 @@
 // next MMAs issued (~170): ~950 cycles per block in cycle stamps.  Everything the promotion
 // warps do besides that sits on this path, so the first scales of a tile are fetched one tile
 // ahead and finished rows are handed to other warps instead of being stored by them.
+//
+// In auto mode on ragged groups the launcher runs two kernels: CTA pairs on 256-row tiles, then single CTAs on
+// the groups' last blocks of at most 128 rows (group_row_tiles).  The second is a programmatic dependent of the
+// first (overlap_role): its CTAs start on each SM as the first kernel's CTA there exits.
 #include <cuda_fp8.h>
 
 #include "gg_common.cuh"
